@@ -73,7 +73,7 @@ __device__ __forceinline__ void store_out2(const AttnArgs& a, size_t idx, float 
 // slots), every CTA re-pays set-up, q conversion and merge, and its cp.async ring drains at every CTA boundary.  Here the pages
 // of all (sequence, kv head) pairs form ONE list (pair-major) cut into gridDim.x equal ranges:
 //   * the producer warp streams the range's pages through a ring of K|V stages with 2-D TMA (one 64-row x 128-byte box per
-//     half tile, 128-byte swizzle = the conflict-free ldmatrix layout; SASS UTMALDG) and never stops at a pair boundary;
+//     half tile, 128-byte swizzle = the conflict-free ldmatrix layout) and never stops at a pair boundary;
 //   * 4 consumer warps (16 keys of every page each, mma.sync m16n8k16, heads of the GQA group = the M rows) wait on the stage's
 //     mbarrier, fold the page into their online softmax, release the stage -- no CTA-wide barrier per page;
 //   * a pair that lies inside one range is finished by that CTA alone; a pair that straddles ranges leaves one partial per CTA

@@ -120,7 +120,7 @@ __device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
         : "memory");
     return done != 0;
 }
-// global -> shared bulk async copy (the TMA engine's 1-D mode; SASS: UBLKCP); bytes % 16 == 0, 16-B aligned both sides.
+// global -> shared bulk async copy (the TMA engine's 1-D mode); bytes % 16 == 0, 16-B aligned both sides.
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
                      smem_u32(smem_dst)),
