@@ -11,7 +11,9 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libfastllm_b200.so")
 
-FL_ARCH = {"llama": 0, "mistral": 1, "qwen2": 2, "mixtral": 3, "bert": 4}
+FL_ARCH = {"llama": 0, "mistral": 1, "qwen2": 2, "mixtral": 3, "bert": 4, "nifunex": 5}
+FL_MIXER = {"gla": 0, "latent_attention": 1}
+FL_FFN = {"none": 0, "dense": 1, "moe": 2}
 FL_DTYPE_F32, FL_DTYPE_BF16, FL_DTYPE_F16 = 0, 1, 2
 
 
@@ -22,6 +24,21 @@ class FlConfig(C.Structure):
                 ("sliding_window", C.c_int32), ("qkv_bias", C.c_int32), ("num_local_experts", C.c_int32),
                 ("num_experts_per_tok", C.c_int32), ("norm_eps", C.c_float), ("rope_theta", C.c_double),
                 ("tp_rank", C.c_int32), ("tp_size", C.c_int32), ("ep_dp_attention", C.c_int32), ("reserved", C.c_int32 * 5)]
+
+
+class FlLayerDesc(C.Structure):
+    """fl_layer_desc: one layer of a layered model (mixer + feed-forward, every size and constant)."""
+    _fields_ = [("mixer", C.c_int32), ("heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32), ("decay_rank", C.c_int32),
+                ("tau", C.c_float), ("rot_dim", C.c_int32), ("kv_rank", C.c_int32), ("kv_from", C.c_int32), ("window", C.c_int32),
+                ("rot_dims", C.c_int32), ("rot_base", C.c_double), ("scale", C.c_float), ("yarn_factor", C.c_float),
+                ("yarn_original", C.c_float), ("yarn_fast", C.c_float), ("yarn_slow", C.c_float), ("ffn", C.c_int32), ("ff", C.c_int32),
+                ("limit", C.c_float), ("experts", C.c_int32), ("top", C.c_int32), ("shared_ff", C.c_int32), ("shared_limit", C.c_float),
+                ("reserved", C.c_int32 * 4)]
+
+
+class FlStackConfig(C.Structure):
+    _fields_ = [("arch", C.c_int32), ("vocab", C.c_int32), ("width", C.c_int32), ("n_layers", C.c_int32), ("norm_eps", C.c_float),
+                ("compute_dtype", C.c_int32), ("reserved", C.c_int32 * 6)]
 
 
 class FastllmError(RuntimeError):
@@ -38,6 +55,10 @@ SYMBOLS = {
     "fl_version": (_I, []),
     "fl_device_synchronize": (_I, []),
     "fl_model_create": (_I, [C.POINTER(FlConfig), C.POINTER(_VP)]),
+    "fl_model_create_layered": (_I, [C.POINTER(FlStackConfig), C.POINTER(FlLayerDesc), C.POINTER(_VP)]),
+    "fl_cache_create_pooled": (_I, [_VP, _I, _I, _I, C.POINTER(_VP)]),
+    "fl_cache_pool_stats": (_I, [_VP, C.POINTER(_I), C.POINTER(_I)]),
+    "fl_forward_ragged": (_I, [_VP, _VP, _VP, _VP, _I, _VP, _VP, _I, _VP]),
     "fl_model_put_tensor": (_I, [_VP, C.c_char_p, _I, C.POINTER(C.c_int64), _I, _VP]),
     "fl_model_random_init": (_I, [_VP, _U64, C.c_float]),
     "fl_model_finalize": (_I, [_VP]),

@@ -1,0 +1,547 @@
+// Layered decoder (FL_ARCH_NIFUNEX): weight layout + ingest, pooled cache (latent pages + recurrent-state slots), and the
+// step function for mixed batches (portions of prompts beside single decoded tokens).
+#include <cmath>
+#include <map>
+
+#include "layered_model.cuh"
+#include "layered_ops.cuh"
+#include "model.cuh"
+#include "synth.cuh"
+
+namespace fl {
+
+static inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+
+static float bits_to_f32(uint16_t b) {
+    const uint32_t u = (uint32_t)b << 16;
+    float f;
+    std::memcpy(&f, &u, 4);
+    return f;
+}
+static uint16_t f32_to_bits(float f) {
+    uint32_t b;
+    std::memcpy(&b, &f, 4);
+    if ((b & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((b >> 16) | 0x40u);
+    return (uint16_t)((b + 0x7FFFu + ((b >> 16) & 1u)) >> 16);
+}
+static float half_to_f32(uint16_t h) {
+    const int e = (h >> 10) & 0x1F, m = h & 0x3FF;
+    float v = e == 0 ? std::ldexp((float)m, -24) : (e == 31 ? (m ? NAN : INFINITY) : std::ldexp((float)(m + 1024), e - 25));
+    return (h & 0x8000) ? -v : v;
+}
+
+// where a named tensor goes
+struct LyRoute {
+    enum Kind { MAT16, F32, UK_T } kind;
+    void* dst;
+    int64_t rows, cols;     // shape handed over
+    int heads;              // UK_T: source rows = heads * (rows / heads)
+};
+struct LayeredRoutes {
+    std::map<std::string, LyRoute> r;
+};
+static std::map<const LayeredModel*, LayeredRoutes> g_routes;      // built with the model, dropped at finalize
+static std::mutex g_routes_mu;
+
+static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
+    const std::string at = "layer " + std::to_string(i) + ": ";
+    FL_CHECK(d.heads >= 1 && d.dim >= 1 && d.vdim >= 1, FL_ERR_INVALID, at + "heads / dim / vdim must be positive");
+    if (d.mixer == FL_MIXER_GLA) {
+        FL_CHECK(d.decay_rank >= 1 && d.decay_rank <= 4096 && d.tau > 0.f, FL_ERR_INVALID, at + "bad decay rank / tau");
+        FL_CHECK(d.dim <= 256, FL_ERR_UNSUPPORTED, at + "gated linear attention: at most 256 key channels per head");
+    } else if (d.mixer == FL_MIXER_LATENT_ATTN) {
+        FL_CHECK(d.kv_rank >= 1 && d.kv_rank <= 512 && d.rot_dim >= 0 && d.rot_dim <= 128, FL_ERR_UNSUPPORTED,
+                 at + "latent attention: kv_rank <= 512 and rot_dim <= 128");
+        FL_CHECK(d.rot_dims >= 0 && d.rot_dims <= d.rot_dim && d.rot_dims % 2 == 0, FL_ERR_INVALID, at + "rotated channels must be even and <= rot_dim");
+        FL_CHECK(d.window >= 0, FL_ERR_INVALID, at + "negative window");
+        if (d.kv_from >= 0) {
+            FL_CHECK(d.kv_from < i, FL_ERR_INVALID, at + "kv_from must name an earlier layer");
+            const fl_layer_desc& s = m.layers[d.kv_from].d;
+            FL_CHECK(s.mixer == FL_MIXER_LATENT_ATTN && s.kv_from < 0 && s.kv_rank == d.kv_rank && s.rot_dim == d.rot_dim &&
+                         s.rot_dims == d.rot_dims && s.rot_base == d.rot_base && s.yarn_factor == d.yarn_factor &&
+                         s.yarn_original == d.yarn_original && s.yarn_fast == d.yarn_fast && s.yarn_slow == d.yarn_slow,
+                     FL_ERR_INVALID, at + "kv_from must name a latent-attention layer with its own cache and the same latent / rotary sizes");
+        }
+    } else {
+        FL_CHECK(false, FL_ERR_INVALID, at + "unknown mixer");
+    }
+    if (d.ffn == FL_FFN_DENSE) {
+        FL_CHECK(d.ff >= 1, FL_ERR_INVALID, at + "ff must be positive");
+    } else if (d.ffn == FL_FFN_MOE) {
+        FL_CHECK(d.ff >= 1 && d.experts >= 1 && d.experts <= 1024 && d.top >= 1 && d.top <= d.experts && d.shared_ff >= 0, FL_ERR_INVALID,
+                 at + "bad expert counts");
+    } else {
+        FL_CHECK(d.ffn == FL_FFN_NONE, FL_ERR_INVALID, at + "unknown feed-forward kind");
+    }
+}
+
+void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
+    const fl_stack_config& c = m.cfg;
+    FL_CHECK(c.arch == FL_ARCH_NIFUNEX, FL_ERR_INVALID, "layered models: unknown arch");
+    FL_CHECK(c.vocab >= 1 && c.width >= 1 && c.n_layers >= 1 && c.n_layers <= 4096, FL_ERR_INVALID, "layered models: sizes must be positive");
+    FL_CHECK(c.compute_dtype == FL_DTYPE_BF16 || c.compute_dtype == FL_DTYPE_F32, FL_ERR_INVALID, "compute_dtype must be bf16 or f32");
+    m.W = c.width; m.V = c.vocab; m.L = c.n_layers; m.f32 = c.compute_dtype == FL_DTYPE_F32;
+    m.layers.resize(m.L);
+    struct Reg { void** pp; size_t bytes; };
+    std::vector<Reg> regs;
+    auto reg = [&](auto** pp, size_t bytes) { regs.push_back({(void**)pp, bytes}); };
+    const size_t W = m.W;
+    reg(&m.embed, (size_t)m.V * W * 2); reg(&m.head, (size_t)m.V * W * 2); reg(&m.final_norm, W * 4);
+    for (int i = 0; i < m.L; ++i) {
+        LayeredLayerW& lw = m.layers[i];
+        lw.d = descs[i];
+        const fl_layer_desc& d = lw.d;
+        check_layer(m, i, d);
+        const size_t H = d.heads, D = d.dim, Dv = d.vdim;
+        reg(&lw.norm1, W * 4); reg(&lw.norm1b, W * 4);
+        if (d.mixer == FL_MIXER_GLA) {
+            lw.off_q = 0; lw.off_k = (int)(H * D); lw.off_v = (int)(2 * H * D); lw.off_g = lw.off_v + (int)(H * Dv);
+            lw.off_a = lw.off_g + (int)(H * Dv);
+            lw.n_in = lw.off_a + d.decay_rank;
+            reg(&lw.a2, H * D * d.decay_rank * 4); reg(&lw.a2b, H * D * 4); reg(&lw.hnorm, Dv * 4);
+            lw.gla_index = (int)m.gla_layers.size();
+            m.gla_layers.push_back(i);
+            m.max_hd = std::max<int>(m.max_hd, (int)(H * D));
+        } else {
+            const size_t R = d.rot_dim, C = d.kv_rank;
+            lw.off_q = 0; lw.n_in = (int)(H * (D + R));
+            lw.off_dkv = -1;
+            if (d.kv_from < 0) {
+                lw.off_dkv = lw.n_in; lw.n_in += (int)(C + R);
+                reg(&lw.dkv_norm, C * 4);
+                lw.kv_owner = i;
+                lw.kv_index = (int)m.kv_layers.size();
+                m.kv_layers.push_back(i);
+            } else {
+                lw.kv_owner = d.kv_from;
+                lw.kv_index = m.layers[d.kv_from].kv_index;
+            }
+            reg(&lw.uk_t, H * C * D * 2); reg(&lw.uv, H * Dv * C * 2);
+            const RopeSpec rs{d.rot_dims, d.rot_base, d.yarn_factor, d.yarn_original, d.yarn_fast, d.yarn_slow};
+            int ri = -1;
+            for (size_t k = 0; k < m.ropes.size(); ++k)
+                if (m.ropes[k] == rs) ri = (int)k;
+            if (ri < 0) { ri = (int)m.ropes.size(); m.ropes.push_back(rs); }
+            lw.rope_index = ri;
+            m.max_hc = std::max<int>(m.max_hc, (int)(H * C));
+        }
+        reg(&lw.w_in, (size_t)lw.n_in * W * 2);
+        reg(&lw.w_o, W * H * Dv * 2);
+        m.max_in = std::max(m.max_in, lw.n_in);
+        m.max_hv = std::max<int>(m.max_hv, (int)(H * Dv));
+        if (d.ffn != FL_FFN_NONE) {
+            reg(&lw.norm2, W * 4); reg(&lw.norm2b, W * 4);
+            const size_t G = d.ffn == FL_FFN_MOE ? d.experts : 1, F = d.ff;
+            reg(&lw.w_gu, G * 2 * F * W * 2); reg(&lw.w_down, G * W * F * 2);
+            m.max_ff = std::max<int>(m.max_ff, (int)F);
+            m.max_top = std::max(m.max_top, d.ffn == FL_FFN_MOE ? d.top : 1);
+            if (d.ffn == FL_FFN_MOE) {
+                reg(&lw.router, (size_t)d.experts * W * 4);
+                m.max_experts = std::max(m.max_experts, d.experts);
+                if (d.shared_ff > 0) {
+                    reg(&lw.s_gu, (size_t)2 * d.shared_ff * W * 2); reg(&lw.s_down, W * (size_t)d.shared_ff * 2);
+                    reg(&lw.shared_gate, W * 4);
+                    m.max_ff = std::max(m.max_ff, d.shared_ff);
+                }
+            }
+        }
+    }
+    size_t total = 0;
+    for (const Reg& r : regs) total += up256(r.bytes);
+    m.slab.alloc(total, /*zero=*/true);
+    size_t off = 0;
+    for (const Reg& r : regs) { *r.pp = m.slab.p + off; off += up256(r.bytes); }
+    m.weight_bytes = total - up256((size_t)m.V * W * 2);
+
+    // names -> destinations
+    LayeredRoutes R;
+    auto mat = [&](const std::string& n, uint16_t* base, int64_t row0, int64_t rows, int64_t cols) {
+        R.r[n] = LyRoute{LyRoute::MAT16, base + row0 * cols, rows, cols, 0};
+    };
+    auto vec = [&](const std::string& n, float* base, int64_t rows, int64_t cols) { R.r[n] = LyRoute{LyRoute::F32, base, rows, cols, 0}; };
+    mat("embed", m.embed, 0, m.V, W); mat("head", m.head, 0, m.V, W); vec("final.norm", m.final_norm, W, 1);
+    for (int i = 0; i < m.L; ++i) {
+        LayeredLayerW& lw = m.layers[i];
+        const fl_layer_desc& d = lw.d;
+        const std::string p = "l" + std::to_string(i) + ".";
+        const int64_t H = d.heads, D = d.dim, Dv = d.vdim;
+        vec(p + "norm1", lw.norm1, W, 1); vec(p + "norm1b", lw.norm1b, W, 1);
+        if (d.mixer == FL_MIXER_GLA) {
+            mat(p + "mix.q", lw.w_in, lw.off_q, H * D, W); mat(p + "mix.k", lw.w_in, lw.off_k, H * D, W);
+            mat(p + "mix.v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "mix.g", lw.w_in, lw.off_g, H * Dv, W);
+            mat(p + "mix.a1", lw.w_in, lw.off_a, d.decay_rank, W);
+            vec(p + "mix.a2", lw.a2, H * D, d.decay_rank); vec(p + "mix.a2.b", lw.a2b, H * D, 1); vec(p + "mix.norm", lw.hnorm, Dv, 1);
+        } else {
+            const int64_t Rr = d.rot_dim, C = d.kv_rank;
+            mat(p + "mix.q", lw.w_in, 0, H * (D + Rr), W);
+            if (d.kv_from < 0) { mat(p + "mix.dkv", lw.w_in, lw.off_dkv, C + Rr, W); vec(p + "mix.dkv.norm", lw.dkv_norm, C, 1); }
+            R.r[p + "mix.uk"] = LyRoute{LyRoute::UK_T, lw.uk_t, H * D, C, (int)H};
+            mat(p + "mix.uv", lw.uv, 0, H * Dv, C);
+        }
+        mat(p + "mix.o", lw.w_o, 0, W, H * Dv);
+        if (d.ffn == FL_FFN_NONE) continue;
+        vec(p + "norm2", lw.norm2, W, 1); vec(p + "norm2b", lw.norm2b, W, 1);
+        const int64_t F = d.ff;
+        if (d.ffn == FL_FFN_DENSE) {
+            mat(p + "mlp.gate", lw.w_gu, 0, F, W); mat(p + "mlp.up", lw.w_gu, F, F, W); mat(p + "mlp.down", lw.w_down, 0, W, F);
+        } else {
+            vec(p + "mlp.router", lw.router, d.experts, W);
+            for (int e = 0; e < d.experts; ++e) {
+                const std::string q = p + "mlp.e" + std::to_string(e) + ".";
+                mat(q + "gate", lw.w_gu, (int64_t)e * 2 * F, F, W); mat(q + "up", lw.w_gu, (int64_t)e * 2 * F + F, F, W);
+                mat(q + "down", lw.w_down, (int64_t)e * W, W, F);
+            }
+            if (d.shared_ff > 0) {
+                const int64_t Fs = d.shared_ff;
+                mat(p + "mlp.shared.gate", lw.s_gu, 0, Fs, W); mat(p + "mlp.shared.up", lw.s_gu, Fs, Fs, W);
+                mat(p + "mlp.shared.down", lw.s_down, 0, W, Fs); vec(p + "mlp.shared.sg", lw.shared_gate, 1, W);
+            }
+        }
+    }
+    for (const auto& kv : R.r) m.expected.push_back(kv.first);
+    std::lock_guard<std::mutex> g(g_routes_mu);
+    g_routes[&m] = std::move(R);
+}
+
+static const LyRoute* find_route(const LayeredModel& m, const std::string& name) {
+    std::lock_guard<std::mutex> g(g_routes_mu);
+    auto it = g_routes.find(&m);
+    if (it == g_routes.end()) return nullptr;
+    auto jt = it->second.r.find(name);
+    return jt == it->second.r.end() ? nullptr : &jt->second;
+}
+
+void layered_put_tensor(LayeredModel& m, const char* name, int dtype, const int64_t* shape, int rank, const void* host) {
+    FL_CHECK(!m.finalized, FL_ERR_STATE, "model already finalized");
+    const LyRoute* r = find_route(m, name);
+    if (r == nullptr) { m.ignored++; return; }       // a tensor the layers do not read
+    int64_t numel = 1;
+    for (int i = 0; i < rank; ++i) numel *= shape[i];
+    const bool shape_ok = numel == r->rows * r->cols && (rank == 1 || (rank == 2 && (shape[0] == r->rows || r->cols == 1 || r->rows == 1)));
+    FL_CHECK(shape_ok, FL_ERR_INVALID, std::string("shape mismatch for ") + name);
+    FL_CHECK(dtype == FL_DTYPE_F32 || dtype == FL_DTYPE_BF16 || dtype == FL_DTYPE_F16, FL_ERR_INVALID, "bad dtype");
+    std::vector<uint16_t> bits((size_t)numel);
+    if (dtype == FL_DTYPE_BF16) std::memcpy(bits.data(), host, (size_t)numel * 2);
+    else if (dtype == FL_DTYPE_F32) for (int64_t i = 0; i < numel; ++i) bits[i] = f32_to_bits(((const float*)host)[i]);
+    else for (int64_t i = 0; i < numel; ++i) bits[i] = f32_to_bits(half_to_f32(((const uint16_t*)host)[i]));
+    if (r->kind == LyRoute::MAT16) {
+        FL_CUDA(cudaMemcpy(r->dst, bits.data(), (size_t)numel * 2, cudaMemcpyHostToDevice));
+    } else if (r->kind == LyRoute::F32) {
+        std::vector<float> v((size_t)numel);
+        for (int64_t i = 0; i < numel; ++i) v[i] = bits_to_f32(bits[i]);
+        FL_CUDA(cudaMemcpy(r->dst, v.data(), (size_t)numel * 4, cudaMemcpyHostToDevice));
+    } else {        // [heads * D, C] -> [heads][C][D]
+        const int64_t Hh = r->heads, D = r->rows / Hh, C = r->cols;
+        std::vector<uint16_t> t((size_t)numel);
+        for (int64_t h = 0; h < Hh; ++h)
+            for (int64_t d = 0; d < D; ++d)
+                for (int64_t c = 0; c < C; ++c) t[(size_t)((h * C + c) * D + d)] = bits[(size_t)((h * D + d) * C + c)];
+        FL_CUDA(cudaMemcpy(r->dst, t.data(), (size_t)numel * 2, cudaMemcpyHostToDevice));
+    }
+    m.have.insert(name);
+}
+
+void layered_random_init(LayeredModel& m, uint64_t seed, float stdv) {
+    FL_CHECK(!m.finalized, FL_ERR_STATE, "model already finalized");
+    const RowMap ident{0, 0, 0, 0};
+    for (const std::string& n : m.expected) {
+        const LyRoute* r = find_route(m, n);
+        const uint64_t ts = tensor_seed(seed, n.c_str());
+        const int64_t numel = r->rows * r->cols;
+        if (r->kind == LyRoute::F32) {
+            const bool around_one = n.size() >= 8 && (n.compare(n.size() - 8, 8, "mix.norm") == 0 || n.compare(n.size() - 8, 8, "dkv.norm") == 0);
+            const bool is_mat = n.find("router") != std::string::npos || n.find("mix.a2") != std::string::npos || n.find("shared.sg") != std::string::npos;
+            const bool is_bias = n.size() >= 4 && n.compare(n.size() - 4, 4, "a2.b") == 0;
+            if (around_one) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 1.0f);
+            else if (is_bias) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 3.0f);
+            else if (is_mat) synth_fill_f32_kernel<<<kNumSMs, 256>>>((float*)r->dst, numel, ts, stdv, ident);
+            else fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 0.0f);
+        } else {
+            synth_fill_bf16_kernel<<<kNumSMs * 8, 256>>>((uint16_t*)r->dst, 1, numel, numel, ts, n == "embed" ? 1.0f : stdv, ident);
+        }
+        g_launches.fetch_add(1);
+        m.have.insert(n);
+    }
+    FL_CUDA(cudaGetLastError());
+    FL_CUDA(cudaDeviceSynchronize());
+}
+
+void layered_finalize(LayeredModel& m) {
+    FL_CHECK(!m.finalized, FL_ERR_STATE, "model already finalized");
+    for (const std::string& n : m.expected) FL_CHECK(m.have.count(n), FL_ERR_STATE, "missing tensor: " + n);
+    {
+        std::lock_guard<std::mutex> g(g_routes_mu);
+        g_routes.erase(&m);
+    }
+    m.finalized = true;
+}
+
+// ---- cache -------------------------------------------------------------------------------------------------------------------
+static void rope_tables(const RopeSpec& rs, int max_seq, std::vector<float>& cs, std::vector<float>& sn) {
+    const int half = rs.dims / 2;
+    std::vector<double> f(half);
+    double mult = 1.0;
+    for (int i = 0; i < half; ++i) f[i] = std::pow(rs.base, -2.0 * i / (double)rs.dims);
+    if (rs.yarn_factor > 0.f) {
+        // YaRN: pairs that complete many turns inside the original context keep their frequency, slow pairs are stretched by the
+        // factor, a linear ramp between the two pair indices; cos and sin grow by 0.1 ln(factor) + 1
+        const double factor = rs.yarn_factor, orig = rs.yarn_original;
+        auto corr = [&](double turns) { return rs.dims * std::log(orig / (2.0 * M_PI * turns)) / (2.0 * std::log(rs.base)); };
+        const double lo = std::max(std::floor(corr(rs.yarn_fast)), 0.0), hi = std::min(std::ceil(corr(rs.yarn_slow)), (double)rs.dims - 1.0);
+        for (int i = 0; i < half; ++i) {
+            const double ramp = std::min(1.0, std::max(0.0, (i - lo) / std::max(hi - lo, 0.001)));
+            f[i] = f[i] / factor * ramp + f[i] * (1.0 - ramp);
+        }
+        mult = 0.1 * std::log(factor) + 1.0;
+    }
+    cs.resize((size_t)max_seq * half); sn.resize((size_t)max_seq * half);
+    for (int p = 0; p < max_seq; ++p)
+        for (int i = 0; i < half; ++i) {
+            cs[(size_t)p * half + i] = (float)(std::cos(p * f[i]) * mult);
+            sn[(size_t)p * half + i] = (float)(std::sin(p * f[i]) * mult);
+        }
+}
+
+void layered_cache_create(fl_cache& c, int max_slots, int max_seq, int pool_tokens) {
+    const LayeredModel& m = *c.lm;
+    FL_CHECK(m.finalized, FL_ERR_STATE, "model not finalized");
+    FL_CHECK(max_slots >= 1 && max_slots <= kMaxBatch && max_seq >= 1 && pool_tokens >= 1, FL_ERR_INVALID, "bad cache dimensions");
+    c.max_batch = max_slots; c.max_seq = max_seq;
+    c.pages_per_seq = (max_seq + kKvPage - 1) / kKvPage;
+    FL_CUDA(cudaStreamCreateWithFlags(&c.stream, cudaStreamNonBlocking));
+    c.ly.reset(new LayeredCache);
+    LayeredCache& y = *c.ly;
+    y.f32 = m.f32;
+    const int pages = (pool_tokens + kKvPage - 1) / kKvPage;
+    y.pool = PagePool(pages, max_slots, c.pages_per_seq, kKvPage);
+    const size_t esz = m.f32 ? 4 : 2;
+    y.kv_store.resize(m.kv_layers.size());
+    for (size_t k = 0; k < m.kv_layers.size(); ++k) {
+        const fl_layer_desc& d = m.layers[m.kv_layers[k]].d;
+        y.kv_store[k].alloc((size_t)pages * kKvPage * (d.kv_rank + d.rot_dim) * esz, true);
+        y.kv_pool.push_back(y.kv_store[k].p);
+    }
+    y.gla_state.resize(m.gla_layers.size());
+    for (size_t k = 0; k < m.gla_layers.size(); ++k) {
+        const fl_layer_desc& d = m.layers[m.gla_layers[k]].d;
+        y.gla_state[k].alloc((size_t)max_slots * d.heads * d.dim * d.vdim, true);
+    }
+    y.rope_cos.resize(m.ropes.size()); y.rope_sin.resize(m.ropes.size());
+    for (size_t k = 0; k < m.ropes.size(); ++k) {
+        std::vector<float> cs, sn;
+        rope_tables(m.ropes[k], max_seq, cs, sn);
+        y.rope_cos[k].alloc(std::max<size_t>(cs.size(), 1)); y.rope_sin[k].alloc(std::max<size_t>(sn.size(), 1));
+        if (!cs.empty()) {
+            FL_CUDA(cudaMemcpy(y.rope_cos[k].p, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+            FL_CUDA(cudaMemcpy(y.rope_sin[k].p, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+        }
+    }
+    y.page_table.alloc((size_t)max_slots * c.pages_per_seq, true);
+    c.slot_len.assign(max_slots, 0);
+    FL_CUDA(cudaDeviceSynchronize());
+}
+
+void layered_slot_reset(fl_cache& c, int slot) {
+    c.ly->pool.release(slot);       // the recurrent state needs no clearing: a sequence that starts at position 0 starts from zero
+    c.slot_len[slot] = 0;
+}
+
+void layered_cache_reset(fl_cache& c) {
+    for (int s = 0; s < c.max_batch; ++s) layered_slot_reset(c, s);
+}
+
+static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
+    const LayeredModel& m = *c.lm;
+    LayeredCache& y = *c.ly;
+    if (T > y.rows) {
+        FL_CUDA(cudaStreamSynchronize(c.stream));
+        const size_t R = std::max<size_t>(T, 2 * y.rows), W = m.W, P = R * std::max(m.max_top, 1);
+        y.x.alloc(R * W); y.h.alloc(R * W); y.y.alloc(R * W);
+        y.proj.alloc(R * m.max_in); y.u.alloc(R * std::max(m.max_hv, 1)); y.go.alloc(R * std::max(m.max_hv, 1));
+        y.la.alloc(R * std::max(m.max_hd, 1));
+        y.qa.alloc(R * std::max(m.max_hc, 1)); y.ol.alloc(R * std::max(m.max_hc, 1));
+        y.gu.alloc(P * 2 * std::max(m.max_ff, 1)); y.act.alloc(P * std::max(m.max_ff, 1)); y.eo.alloc(P * W);
+        y.sh_gu.alloc(R * 2 * std::max(m.max_ff, 1)); y.sh_act.alloc(R * std::max(m.max_ff, 1)); y.sh_o.alloc(R * W);
+        y.route_w.alloc(P); y.route_sel.alloc(P); y.sgate.alloc(R);
+        y.pair_row.alloc(P); y.pair_of.alloc(P); y.grp_off.alloc((size_t)m.max_experts + 2);
+        y.rows = R;
+    }
+    if (n_want > y.want_cap) {
+        FL_CUDA(cudaStreamSynchronize(c.stream));
+        const size_t N = std::max<size_t>(n_want, 2 * y.want_cap);
+        y.hf.alloc(N * m.W); y.logits.alloc(N * m.V); y.h_logits.alloc(N * m.V);
+        y.want_cap = N;
+    }
+}
+
+static void gemm(LaunchCtx& lc, const char* tag, const float* A, int lda, const uint16_t* Wt, int N, int K, float* Y, int ldy, int R) {
+    if (R <= 0) return;
+    LyGemm g{A, 0, lda, nullptr, Wt, 0, N, K, Y, 0, ldy, nullptr, R};
+    launch(lc, tag, (uint64_t)N * K * 2, ly_gemm_kernel, dim3((N + kLyBN - 1) / kLyBN, (R + kLyBM - 1) / kLyBM, 1), dim3(256), 0, g);
+}
+static void gemm_groups(LaunchCtx& lc, const char* tag, const LyGemm& g, int groups, int max_rows) {
+    if (max_rows <= 0) return;
+    launch(lc, tag, (uint64_t)groups * g.N * g.K * 2, ly_gemm_kernel, dim3((g.N + kLyBN - 1) / kLyBN, (max_rows + kLyBM - 1) / kLyBM, groups),
+           dim3(256), 0, g);
+}
+
+template <typename CT>
+static void launch_latent_attn(LaunchCtx& lc, const LatentAttnArgs& a, int T) {
+    const int cpl = (a.C + 31) / 32;
+    const size_t smem = ((size_t)kLatWarps * a.C + 2 * kLatWarps) * 4;
+    const dim3 g(T, a.H), b(kLatWarps * 32);
+    const uint64_t bytes = 0;
+    if (cpl <= 1) launch(lc, "latent_attn", bytes, ly_latent_attn_kernel<CT, 1>, g, b, smem, a);
+    else if (cpl <= 2) launch(lc, "latent_attn", bytes, ly_latent_attn_kernel<CT, 2>, g, b, smem, a);
+    else if (cpl <= 4) launch(lc, "latent_attn", bytes, ly_latent_attn_kernel<CT, 4>, g, b, smem, a);
+    else if (cpl <= 8) launch(lc, "latent_attn", bytes, ly_latent_attn_kernel<CT, 8>, g, b, smem, a);
+    else launch(lc, "latent_attn", bytes, ly_latent_attn_kernel<CT, 16>, g, b, smem, a);
+}
+
+static void launch_gla_scan(LaunchCtx& lc, const GlaArgs& a, int n) {
+    const int rpt = (a.D + kGlaDG - 1) / kGlaDG;
+    const size_t smem = ((size_t)6 * a.D + 2 * kGlaVS + 2 * kGlaDG * kGlaVS) * 4;
+    const dim3 g(n, a.H, (a.Dv + kGlaVS - 1) / kGlaVS), b(kGlaVS * kGlaDG);
+    if (rpt <= 1) launch(lc, "gla_scan", 0, ly_gla_scan_kernel<1>, g, b, smem, a);
+    else if (rpt <= 2) launch(lc, "gla_scan", 0, ly_gla_scan_kernel<2>, g, b, smem, a);
+    else if (rpt <= 4) launch(lc, "gla_scan", 0, ly_gla_scan_kernel<4>, g, b, smem, a);
+    else if (rpt <= 8) launch(lc, "gla_scan", 0, ly_gla_scan_kernel<8>, g, b, smem, a);
+    else if (rpt <= 16) launch(lc, "gla_scan", 0, ly_gla_scan_kernel<16>, g, b, smem, a);
+    else launch(lc, "gla_scan", 0, ly_gla_scan_kernel<32>, g, b, smem, a);
+}
+
+void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, const uint32_t* ids, const int* want, int n_want) {
+    const LayeredModel& m = *c.lm;
+    LayeredCache& y = *c.ly;
+    FL_CHECK(!c.poisoned, FL_ERR_CUDA, "cache poisoned by an earlier CUDA error");
+    FL_CHECK(slots && counts && ids && (want || n_want == 0), FL_ERR_INVALID, "NULL argument");
+    FL_CHECK(n >= 1 && n <= c.max_batch && n_want >= 0, FL_ERR_INVALID, "bad batch");
+    // ---- host: validate, take pages, lay out the step tables ----
+    long long T = 0;
+    std::vector<char> seen(c.max_batch, 0);
+    int need_pages = 0;
+    for (int i = 0; i < n; ++i) {
+        const int sl = slots[i];
+        FL_CHECK(sl >= 0 && sl < c.max_batch, FL_ERR_INVALID, "slot index out of range");
+        FL_CHECK(!seen[sl], FL_ERR_INVALID, "a slot appears twice in one call");
+        seen[sl] = 1;
+        FL_CHECK(counts[i] >= 1, FL_ERR_INVALID, "every sequence of a step brings at least one token");
+        FL_CHECK(c.slot_len[sl] + counts[i] <= c.max_seq, FL_ERR_STATE, "sequence longer than the cache's max_seq");
+        need_pages += y.pool.missing(sl, c.slot_len[sl] + counts[i]);
+        T += counts[i];
+    }
+    FL_CHECK(need_pages <= y.pool.pages_free(), FL_ERR_STATE, "cache page pool exhausted");
+    for (long long i = 0; i < T; ++i) FL_CHECK(ids[i] < (uint32_t)m.V, FL_ERR_INVALID, "token id out of range");
+    for (int k = 0; k < n_want; ++k) FL_CHECK(want[k] >= 0 && want[k] < T, FL_ERR_INVALID, "wanted row out of range");
+    ensure_ws(c, (size_t)T, (size_t)n_want);
+    const size_t tab_ints = (size_t)3 * T + 3 * (size_t)n + 1 + (size_t)n_want;
+    if (tab_ints > y.tab_cap) {
+        FL_CUDA(cudaStreamSynchronize(c.stream));
+        y.tab_cap = std::max(tab_ints, 2 * y.tab_cap);
+        y.step_tab.alloc(y.tab_cap); y.h_step_tab.alloc(y.tab_cap);
+    }
+    FL_CUDA(cudaStreamSynchronize(c.stream));      // the pinned staging buffers of the previous step are free again
+    int* ht = y.h_step_tab.p;
+    int *h_tok = ht, *h_rseq = ht + T, *h_rpos = ht + 2 * T, *h_row0 = ht + 3 * T, *h_slot = h_row0 + n + 1, *h_pos0 = h_slot + n,
+        *h_want = h_pos0 + n;
+    int row = 0;
+    for (int i = 0; i < n; ++i) {
+        const int sl = slots[i];
+        h_row0[i] = row; h_slot[i] = sl; h_pos0[i] = c.slot_len[sl];
+        for (int k = 0; k < counts[i]; ++k, ++row) { h_tok[row] = (int)ids[row]; h_rseq[row] = i; h_rpos[row] = c.slot_len[sl] + k; }
+        const int before = y.pool.held(sl);
+        y.pool.grow(sl, c.slot_len[sl] + counts[i]);
+        if (y.pool.held(sl) != before)
+            FL_CUDA(cudaMemcpyAsync(y.page_table.p + (size_t)sl * c.pages_per_seq + before, y.pool.row(sl) + before,
+                                    (size_t)(y.pool.held(sl) - before) * 4, cudaMemcpyHostToDevice, c.stream));
+    }
+    h_row0[n] = row;
+    for (int k = 0; k < n_want; ++k) h_want[k] = want[k];
+    FL_CUDA(cudaMemcpyAsync(y.step_tab.p, ht, tab_ints * 4, cudaMemcpyHostToDevice, c.stream));
+    const int* dt = y.step_tab.p;
+    StepTab st{dt, dt + T, dt + 2 * T, dt + 3 * T, dt + 3 * T + n + 1, dt + 3 * T + 2 * n + 1, dt + 3 * T + 3 * n + 1, (int)T, n, n_want};
+
+    // ---- device: layer by layer over all rows of the step ----
+    LaunchCtx lc;
+    lc.stream = c.stream;
+    lc.pdl = false;
+    const int Ti = (int)T, W = m.W;
+    const float eps = m.cfg.norm_eps;
+    const int nthr = std::min(1024, std::max(64, (W + 31) / 32 * 32));
+    launch(lc, "embed_norm", 0, ly_embed_norm_kernel, dim3(Ti), dim3(nthr), 0, (const uint16_t*)m.embed, st.tok, W, (const float*)m.layers[0].norm1, eps,
+           y.x.p, y.h.p);
+    for (int li = 0; li < m.L; ++li) {
+        const LayeredLayerW& lw = m.layers[li];
+        const fl_layer_desc& d = lw.d;
+        const int H = d.heads, D = d.dim, Dv = d.vdim;
+        gemm(lc, "gemm_mix_in", y.h.p, W, lw.w_in, lw.n_in, W, y.proj.p, lw.n_in, Ti);
+        if (d.mixer == FL_MIXER_GLA) {
+            launch(lc, "gla_decay", 0, ly_gla_decay_kernel, dim3(Ti), dim3(256), (size_t)d.decay_rank * 4, (const float*)y.proj.p, lw.n_in, lw.off_a,
+                   d.decay_rank, (const float*)lw.a2, (const float*)lw.a2b, H * D, 1.f / d.tau, y.la.p);
+            GlaArgs ga{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, y.la.p, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0, st.seq_slot,
+                       st.seq_pos0, H, D, Dv, (float)(1.0 / std::sqrt((double)D))};
+            launch_gla_scan(lc, ga, n);
+            launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)ga.o, (const float*)y.proj.p, lw.n_in, lw.off_g,
+                   (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p);
+        } else {
+            const int R = d.rot_dim, C = d.kv_rank;
+            LatentAppendArgs aa{y.proj.p, lw.n_in, lw.off_q, lw.off_dkv, lw.dkv_norm, eps, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq,
+                                st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p, H, D, R, C, d.rot_dims};
+            if (m.f32) launch(lc, "latent_append", 0, ly_latent_append_kernel<float>, dim3(Ti), dim3(128), 0, aa);
+            else launch(lc, "latent_append", 0, ly_latent_append_kernel<uint16_t>, dim3(Ti), dim3(128), 0, aa);
+            // q~[row, h, :] = W_uk[h]^T q_plain[row, h, :]: the score against the latent needs no per-head keys
+            LyGemm qa{y.proj.p + lw.off_q, D + R, lw.n_in, nullptr, lw.uk_t, (long long)C * D, C, D, y.qa.p, C, H * C, nullptr, Ti};
+            gemm_groups(lc, "gemm_q_absorb", qa, H, Ti);
+            LatentAttnArgs at{y.qa.p, y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos,
+                              st.seq_slot, y.ol.p, H, D, R, C, d.window, d.scale};
+            if (m.f32) launch_latent_attn<float>(lc, at, Ti); else launch_latent_attn<uint16_t>(lc, at, Ti);
+            // value expansion after the softmax: out[row, h, :] = W_uv[h] (sum_j p_j c_j)
+            LyGemm ov{y.ol.p, C, H * C, nullptr, lw.uv, (long long)Dv * C, Dv, C, y.u.p, Dv, H * Dv, nullptr, Ti};
+            gemm_groups(lc, "gemm_v_expand", ov, H, Ti);
+        }
+        gemm(lc, "gemm_mix_out", y.u.p, H * Dv, lw.w_o, W, H * Dv, y.y.p, W, Ti);
+        const float* next1 = li + 1 < m.L ? m.layers[li + 1].norm1 : nullptr;
+        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm1b,
+               d.ffn != FL_FFN_NONE ? (const float*)lw.norm2 : next1, eps, W, y.h.p);
+        if (d.ffn == FL_FFN_NONE) continue;
+        const int F = d.ff;
+        if (d.ffn == FL_FFN_DENSE) {
+            gemm(lc, "gemm_ff_in", y.h.p, W, lw.w_gu, 2 * F, W, y.gu.p, 2 * F, Ti);
+            launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
+                   (const int*)nullptr, Ti, y.act.p);
+            gemm(lc, "gemm_ff_out", y.act.p, F, lw.w_down, W, F, y.y.p, W, Ti);
+        } else {
+            const int E = d.experts, top = d.top, P = Ti * top;
+            launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, (const float*)y.h.p, W, (const float*)lw.router, E, top,
+                   (const float*)lw.shared_gate, y.route_sel.p, y.route_w.p, y.sgate.p);
+            launch(lc, "moe_lists", 0, ly_moe_lists_kernel, dim3(1), dim3(std::min(1024, (E + 31) / 32 * 32)), (size_t)(E + 1) * 4,
+                   (const int*)y.route_sel.p, Ti, top, E, y.grp_off.p, y.pair_row.p, y.pair_of.p);
+            LyGemm g1{y.h.p, 0, W, y.pair_row.p, lw.w_gu, (long long)2 * F * W, 2 * F, W, y.gu.p, 0, 2 * F, y.grp_off.p, P};
+            gemm_groups(lc, "gemm_moe_in", g1, E, P);
+            launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (P * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
+                   (const int*)nullptr, P, y.act.p);
+            LyGemm g2{y.act.p, 0, F, nullptr, lw.w_down, (long long)W * F, W, F, y.eo.p, 0, W, y.grp_off.p, P};
+            gemm_groups(lc, "gemm_moe_out", g2, E, P);
+            const float* sh = nullptr;
+            if (d.shared_ff > 0) {
+                const int Fs = d.shared_ff;
+                gemm(lc, "gemm_shared_in", y.h.p, W, lw.s_gu, 2 * Fs, W, y.sh_gu.p, 2 * Fs, Ti);
+                launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * Fs + 255) / 256)), dim3(256), 0, (const float*)y.sh_gu.p, Fs,
+                       d.shared_limit, (const int*)nullptr, Ti, y.sh_act.p);
+                gemm(lc, "gemm_shared_out", y.sh_act.p, Fs, lw.s_down, W, Fs, y.sh_o.p, W, Ti);
+                sh = y.sh_o.p;
+            }
+            launch(lc, "moe_combine", 0, ly_moe_combine_kernel, dim3((W + 255) / 256, Ti), dim3(256), 0, (const float*)y.eo.p, (const int*)y.pair_of.p,
+                   (const float*)y.route_w.p, top, sh, (const float*)y.sgate.p, W, y.y.p);
+        }
+        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm2b, next1, eps, W, y.h.p);
+    }
+    if (n_want > 0) {
+        launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, y.hf.p);
+        gemm(lc, "gemm_head", y.hf.p, W, m.head, m.V, W, y.logits.p, m.V, n_want);
+        FL_CUDA(cudaMemcpyAsync(y.h_logits.p, y.logits.p, (size_t)n_want * m.V * 4, cudaMemcpyDeviceToHost, c.stream));
+    }
+    for (int i = 0; i < n; ++i) c.slot_len[slots[i]] += counts[i];
+}
+
+}  // namespace fl

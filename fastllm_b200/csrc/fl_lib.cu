@@ -1598,10 +1598,26 @@ FL_EXPORT int fl_model_create(const fl_config* cfg, fl_model** out) {
     FL_API_END
 }
 
+FL_EXPORT int fl_model_create_layered(const fl_stack_config* cfg, const fl_layer_desc* layers, fl_model** out) {
+    FL_API_BEGIN
+    FL_CHECK(cfg != nullptr && layers != nullptr && out != nullptr, FL_ERR_INVALID, "NULL argument");
+    use_device();
+    auto lm = std::make_shared<LayeredModel>();
+    lm->cfg = *cfg;
+    layered_build(*lm, layers);
+    *out = new fl_model{nullptr, nullptr, lm};
+    FL_API_END
+}
+
 FL_EXPORT int fl_model_put_tensor(fl_model* m, const char* name, int dtype, const int64_t* shape, int rank, const void* host_ptr) {
     FL_API_BEGIN
     FL_CHECK(m && name && shape && host_ptr, FL_ERR_INVALID, "NULL argument");
     use_device();
+    if (m->lay) {
+        std::lock_guard<std::mutex> g(m->lay->mu);
+        layered_put_tensor(*m->lay, name, dtype, shape, rank, host_ptr);
+        return FL_OK;
+    }
     if (m->bert) {
         std::lock_guard<std::mutex> g(m->bert->mu);
         bert_put_tensor(*m->bert, name, dtype, shape, rank, host_ptr);
@@ -1616,6 +1632,11 @@ FL_EXPORT int fl_model_random_init(fl_model* m, uint64_t seed, float stdv) {
     FL_API_BEGIN
     FL_CHECK(m, FL_ERR_INVALID, "NULL argument");
     use_device();
+    if (m->lay) {
+        std::lock_guard<std::mutex> g(m->lay->mu);
+        layered_random_init(*m->lay, seed, stdv);
+        return FL_OK;
+    }
     if (m->bert) {
         std::lock_guard<std::mutex> g(m->bert->mu);
         bert_random_init(*m->bert, seed, stdv);
@@ -1630,6 +1651,11 @@ FL_EXPORT int fl_model_finalize(fl_model* m) {
     FL_API_BEGIN
     FL_CHECK(m, FL_ERR_INVALID, "NULL argument");
     use_device();
+    if (m->lay) {
+        std::lock_guard<std::mutex> g(m->lay->mu);
+        layered_finalize(*m->lay);
+        return FL_OK;
+    }
     if (m->bert) {
         std::lock_guard<std::mutex> g(m->bert->mu);
         bert_finalize(*m->bert);
@@ -1643,7 +1669,7 @@ FL_EXPORT int fl_model_finalize(fl_model* m) {
 FL_EXPORT int fl_model_clone(fl_model* m, fl_model** out) {
     FL_API_BEGIN
     FL_CHECK(m && out, FL_ERR_INVALID, "NULL argument");
-    *out = new fl_model{m->w, m->bert};
+    *out = new fl_model{m->w, m->bert, m->lay};
     FL_API_END
 }
 
@@ -1659,14 +1685,58 @@ FL_EXPORT int fl_model_destroy(fl_model* m) {
 FL_EXPORT int fl_model_weight_bytes(fl_model* m, uint64_t* streamed_bytes) {
     FL_API_BEGIN
     FL_CHECK(m && streamed_bytes, FL_ERR_INVALID, "NULL argument");
+    if (m->lay) { *streamed_bytes = m->lay->weight_bytes; return FL_OK; }
     FL_CHECK(m->w != nullptr, FL_ERR_INVALID, "not a causal LM");
     *streamed_bytes = m->w->streamed_bytes;
     FL_API_END
 }
 
+FL_EXPORT int fl_cache_create_pooled(fl_model* m, int max_slots, int max_seq, int pool_tokens, fl_cache** out) {
+    FL_API_BEGIN
+    FL_CHECK(m && out, FL_ERR_INVALID, "NULL argument");
+    FL_CHECK(m->lay != nullptr, FL_ERR_UNSUPPORTED, "pooled caches exist for layered models only");
+    use_device();
+    std::unique_ptr<fl_cache> c(new fl_cache);
+    c->lm = m->lay;
+    layered_cache_create(*c, max_slots, max_seq, pool_tokens);
+    *out = c.release();
+    FL_API_END
+}
+
+FL_EXPORT int fl_cache_pool_stats(fl_cache* c, int* pages_total, int* pages_free) {
+    FL_API_BEGIN
+    FL_CHECK(c && pages_total && pages_free, FL_ERR_INVALID, "NULL argument");
+    FL_CHECK(c->ly != nullptr, FL_ERR_UNSUPPORTED, "pooled caches exist for layered models only");
+    *pages_total = c->ly->pool.pages_total();
+    *pages_free = c->ly->pool.pages_free();
+    FL_API_END
+}
+
+// Layered models behind the uniform entry points: b sequences in slots 0..b-1 (or the given slots), t tokens each, logits of every
+// sequence's last token.  Positions follow from what a slot holds, so the caller's offset must agree with it.
+static void layered_uniform(fl_cache& c, const int* slots, const uint32_t* ids, int n, int t, const size_t* offsets, size_t offset_all,
+                            float* logits_host) {
+    FL_CHECK(ids != nullptr && n >= 1 && n <= c.max_batch && t >= 1, FL_ERR_INVALID, "bad batch / sequence length");
+    std::vector<int> sl(n), cnt(n, t), want(n);
+    for (int i = 0; i < n; ++i) {
+        sl[i] = slots ? slots[i] : i;
+        FL_CHECK(sl[i] >= 0 && sl[i] < c.max_batch, FL_ERR_INVALID, "slot index out of range");
+        const size_t off = offsets ? offsets[i] : offset_all;
+        FL_CHECK((size_t)c.slot_len[sl[i]] == off, FL_ERR_INVALID, "position offset differs from the tokens the sequence already holds");
+        want[i] = i * t + t - 1;
+    }
+    layered_forward(c, sl.data(), cnt.data(), n, ids, want.data(), n);
+    FL_CUDA(cudaStreamSynchronize(c.stream));
+    std::memcpy(logits_host, c.ly->h_logits.p, (size_t)n * c.lm->V * 4);
+}
+
 FL_EXPORT int fl_cache_create(fl_model* m, int max_batch, int max_seq, fl_cache** out) {
     FL_API_BEGIN
     FL_CHECK(m && out, FL_ERR_INVALID, "NULL argument");
+    if (m->lay != nullptr) {
+        FL_CHECK(max_batch >= 1 && max_seq >= 1 && (long long)max_batch * max_seq < (1ll << 31), FL_ERR_INVALID, "bad cache dimensions");
+        return fl_cache_create_pooled(m, max_batch, max_seq, max_batch * ((max_seq + kKvPage - 1) / kKvPage) * kKvPage, out);
+    }
     FL_CHECK(m->w != nullptr, FL_ERR_INVALID, "BERT models have no KV cache");
     use_device();
     std::unique_ptr<fl_cache> c(new fl_cache);
@@ -1680,6 +1750,7 @@ FL_EXPORT int fl_cache_reset(fl_cache* c) {
     FL_API_BEGIN
     FL_CHECK(c, FL_ERR_INVALID, "NULL argument");
     use_device();
+    if (c->ly) { layered_cache_reset(*c); return FL_OK; }
     reset_state_kernel<<<1, 256, 0, c->stream>>>(c->state.p, 0);
     g_launches.fetch_add(1);
     FL_CUDA(cudaStreamSynchronize(c->stream));
@@ -1694,6 +1765,7 @@ FL_EXPORT int fl_cache_slot_reset(fl_cache* c, int slot) {
     FL_CHECK(c, FL_ERR_INVALID, "NULL argument");
     FL_CHECK(slot >= 0 && slot < c->max_batch, FL_ERR_INVALID, "slot index out of range");
     use_device();
+    if (c->ly) { layered_slot_reset(*c, slot); return FL_OK; }
     reset_slot_kernel<<<1, 1, 0, c->stream>>>(c->state.p, slot);
     g_launches.fetch_add(1);
     c->slot_len[slot] = 0;
@@ -1711,6 +1783,7 @@ FL_EXPORT int fl_cache_slot_len(fl_cache* c, int slot, int* out) {
 FL_EXPORT int fl_cache_moe_routing(fl_cache* c, int rows, int32_t* experts, float* margins) {
     FL_API_BEGIN
     FL_CHECK(c && experts && margins, FL_ERR_INVALID, "NULL argument");
+    FL_CHECK(c->w != nullptr, FL_ERR_UNSUPPORTED, "routing records exist for the Mixtral architecture only");
     const Weights& w = *c->w;
     FL_CHECK(w.cfg.arch == FL_ARCH_MIXTRAL, FL_ERR_UNSUPPORTED, "routing records exist for the MoE architecture only");
     FL_CHECK(!c->poisoned, FL_ERR_CUDA, "cache poisoned by an earlier CUDA error");
@@ -1724,6 +1797,7 @@ FL_EXPORT int fl_cache_moe_routing(fl_cache* c, int rows, int32_t* experts, floa
 FL_EXPORT int fl_cache_kv_len(fl_cache* c, int* out) {
     FL_API_BEGIN
     FL_CHECK(c && out, FL_ERR_INVALID, "NULL argument");
+    FL_CHECK(c->ly == nullptr, FL_ERR_UNSUPPORTED, "layered models keep a length per slot: fl_cache_slot_len");
     *out = c->kv_len;
     FL_API_END
 }
@@ -1731,6 +1805,7 @@ FL_EXPORT int fl_cache_kv_len(fl_cache* c, int* out) {
 FL_EXPORT int fl_cache_fill_synthetic(fl_cache* c, int batch, int kv_len, uint64_t seed) {
     FL_API_BEGIN
     FL_CHECK(c, FL_ERR_INVALID, "NULL argument");
+    FL_CHECK(c->ly == nullptr, FL_ERR_UNSUPPORTED, "synthetic fill is not offered for layered models");
     FL_CHECK(batch >= 1 && batch <= c->max_batch && kv_len >= 0 && kv_len <= c->max_seq, FL_ERR_INVALID, "bad synthetic fill size");
     use_device();
     const RowMap ident{0, 0, 0, 0};
@@ -1758,6 +1833,17 @@ FL_EXPORT int fl_cache_destroy(fl_cache* c) {
 FL_EXPORT int fl_forward(fl_model* m, fl_cache* c, const uint32_t* ids, int b, int t, size_t rope_offset, float* logits_host) {
     FL_API_BEGIN
     FL_CHECK(m && c && logits_host, FL_ERR_INVALID, "NULL argument");
+    if (m->lay != nullptr) {
+        FL_CHECK(m->lay.get() == c->lm.get(), FL_ERR_INVALID, "cache belongs to a different model");
+        use_device();
+        try {
+            layered_uniform(*c, nullptr, ids, b, t, nullptr, rope_offset, logits_host);
+        } catch (const fl::Error& e) {
+            if (e.code == FL_ERR_CUDA) c->poisoned = true;
+            throw;
+        }
+        return FL_OK;
+    }
     FL_CHECK(m->w != nullptr && m->w.get() == c->w.get(), FL_ERR_INVALID, "cache belongs to a different model");
     use_device();
     try {
@@ -1908,6 +1994,18 @@ FL_EXPORT int fl_forward_sample(fl_model* m, fl_cache* c, const uint32_t* ids, i
                                 uint32_t* next_id) {
     FL_API_BEGIN
     FL_CHECK(m && c && s && next_id, FL_ERR_INVALID, "NULL argument");
+    if (m->lay != nullptr) {       // layered models: the same call over the mixed-batch step function; row 0 is sampled on the host
+        FL_CHECK(m->lay.get() == c->lm.get(), FL_ERR_INVALID, "cache belongs to a different model");
+        use_device();
+        std::vector<float> lg((size_t)b * m->lay->V);
+        layered_uniform(*c, nullptr, ids, b, t, nullptr, rope_offset, lg.data());
+        try {
+            *next_id = s->lp.sample(lg.data(), (size_t)m->lay->V);
+        } catch (const fl::SamplerError& e) {
+            throw fl::Error(FL_ERR_INVALID, e.what());
+        }
+        return FL_OK;
+    }
     FL_CHECK(m->w != nullptr && m->w.get() == c->w.get(), FL_ERR_INVALID, "cache belongs to a different model");
     use_device();
     try {
@@ -1933,6 +2031,18 @@ FL_EXPORT int fl_forward_slots(fl_model* m, fl_cache* c, const int* slots, const
                                float* logits_host) {
     FL_API_BEGIN
     FL_CHECK(m && c && logits_host, FL_ERR_INVALID, "NULL argument");
+    if (m->lay != nullptr) {
+        FL_CHECK(m->lay.get() == c->lm.get(), FL_ERR_INVALID, "cache belongs to a different model");
+        FL_CHECK(slots && rope_offsets, FL_ERR_INVALID, "NULL argument");
+        use_device();
+        try {
+            layered_uniform(*c, slots, ids, n, t, rope_offsets, 0, logits_host);
+        } catch (const fl::Error& e) {
+            if (e.code == FL_ERR_CUDA) c->poisoned = true;
+            throw;
+        }
+        return FL_OK;
+    }
     FL_CHECK(m->w != nullptr && m->w.get() == c->w.get(), FL_ERR_INVALID, "cache belongs to a different model");
     use_device();
     try {
@@ -1944,6 +2054,25 @@ FL_EXPORT int fl_forward_slots(fl_model* m, fl_cache* c, const int* slots, const
         std::memcpy(logits_host, c->h_logits.p, cnt * 4);
     } catch (const fl::Error& e) {
         if (e.code == FL_ERR_CUDA || e.code == FL_ERR_NCCL) c->poisoned = true;
+        throw;
+    }
+    FL_API_END
+}
+
+FL_EXPORT int fl_forward_ragged(fl_model* m, fl_cache* c, const int* slots, const int* counts, int n, const uint32_t* ids,
+                                const int* want, int n_want, float* logits_host) {
+    FL_API_BEGIN
+    FL_CHECK(m && c, FL_ERR_INVALID, "NULL argument");
+    FL_CHECK(m->lay != nullptr && c->ly != nullptr, FL_ERR_UNSUPPORTED, "mixed batches of unequal portions are offered for layered models only");
+    FL_CHECK(m->lay.get() == c->lm.get(), FL_ERR_INVALID, "cache belongs to a different model");
+    FL_CHECK(n_want == 0 || logits_host != nullptr, FL_ERR_INVALID, "NULL argument");
+    use_device();
+    try {
+        layered_forward(*c, slots, counts, n, ids, want, n_want);
+        FL_CUDA(cudaStreamSynchronize(c->stream));
+        if (n_want > 0) std::memcpy(logits_host, c->ly->h_logits.p, (size_t)n_want * m->lay->V * 4);
+    } catch (const fl::Error& e) {
+        if (e.code == FL_ERR_CUDA) c->poisoned = true;
         throw;
     }
     FL_API_END

@@ -1,0 +1,110 @@
+// Layered decoder (FL_ARCH_NIFUNEX): model / cache objects shared by fl_layered.cu and fl_lib.cu.
+// A layer = one mixer (gated linear attention | latent attention) + an optional feed-forward (dense | MoE with shared expert),
+// each wrapped by a norm before and after.  Sizes and constants come from fl_layer_desc; nothing is fixed per model.
+#pragma once
+#include <cuda.h>
+
+#include <memory>
+#include <mutex>
+#include <set>
+#include <string>
+#include <vector>
+
+#include "../../include/fastllm_b200.h"
+#include "page_pool.hpp"
+#include "runtime.cuh"
+
+namespace fl {
+
+struct LayeredLayerW {
+    fl_layer_desc d{};
+    float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr;     // [W] f32
+    // mixer input projections stacked into ONE matrix [n_in, W] (one GEMM per layer):
+    //   GLA:     q | k | v | g | a1        latent attention:  q | dkv   (no dkv rows when kv_from >= 0)
+    uint16_t* w_in = nullptr;
+    int n_in = 0;
+    int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a = 0, off_dkv = 0;             // row (= output column) offsets inside w_in
+    uint16_t* w_o = nullptr;            // [W, heads * vdim]
+    // GLA
+    float *a2 = nullptr, *a2b = nullptr, *hnorm = nullptr;                               // [heads*dim, rank], [heads*dim], [vdim]
+    // latent attention
+    float* dkv_norm = nullptr;          // [kv_rank]
+    uint16_t* uk_t = nullptr;           // [heads][kv_rank, dim]: W_uk per head, transposed (q absorbs it: q~ = W_uk[h]^T q)
+    uint16_t* uv = nullptr;             // [heads * vdim, kv_rank]
+    int kv_owner = -1;                  // layer whose cache this layer reads (itself when it projects its own)
+    int kv_index = -1;                  // index of that cache among the model's latent caches
+    int rope_index = -1;                // index into the model's distinct rotary tables
+    int gla_index = -1;                 // index among the model's recurrent layers
+    // feed-forward: groups 0..E-1 = experts (or the one dense block), `shared` separate
+    uint16_t *w_gu = nullptr, *w_down = nullptr;        // [groups][2 ff, W] (gate rows then up rows), [groups][W, ff]
+    uint16_t *s_gu = nullptr, *s_down = nullptr;        // shared expert
+    float *router = nullptr, *shared_gate = nullptr;    // [experts, W], [W] f32
+};
+
+struct RopeSpec {                       // one distinct rotary configuration (tables are built per cache: they depend on max_seq)
+    int dims = 0;
+    double base = 0;
+    float yarn_factor = 0, yarn_original = 0, yarn_fast = 0, yarn_slow = 0;
+    bool operator==(const RopeSpec& o) const {
+        return dims == o.dims && base == o.base && yarn_factor == o.yarn_factor && yarn_original == o.yarn_original &&
+               yarn_fast == o.yarn_fast && yarn_slow == o.yarn_slow;
+    }
+};
+
+struct LayeredModel {
+    fl_stack_config cfg{};
+    int W = 0, V = 0, L = 0;
+    bool f32 = false;                   // compute_dtype == FL_DTYPE_F32
+    std::vector<LayeredLayerW> layers;
+    std::vector<RopeSpec> ropes;
+    std::vector<int> kv_layers, gla_layers;            // layers that own a latent cache / a recurrent state
+    DevBuf<uint8_t> slab;
+    uint16_t *embed = nullptr, *head = nullptr;
+    float* final_norm = nullptr;
+    std::set<std::string> have;
+    std::vector<std::string> expected;
+    int ignored = 0;
+    bool finalized = false;
+    uint64_t weight_bytes = 0;
+    // widest sizes over the layers (workspace planning)
+    int max_in = 0, max_hv = 0, max_hd = 0, max_hc = 0, max_ff = 0, max_top = 0, max_experts = 0;
+    std::mutex mu;
+};
+
+// Per-cache state of a layered model: latent-cache pools, recurrent-state slots, rotary tables, step tables, workspace.
+struct LayeredCache {
+    PagePool pool;
+    bool f32 = false;
+    std::vector<void*> kv_pool;         // per latent cache: [pages][64][kv_rank + rot_dim] (float or bf16)
+    std::vector<DevBuf<uint8_t>> kv_store;
+    std::vector<DevBuf<float>> gla_state;          // per recurrent layer: [slots][heads][dim][vdim]
+    std::vector<DevBuf<float>> rope_cos, rope_sin; // per RopeSpec: [max_seq][dims/2]
+    DevBuf<int> page_table;             // [slots][pages_per_slot]
+    DevBuf<int> step_tab;               // per-step integer tables (see StepTab in fl_layered.cu)
+    PinnedBuf<int> h_step_tab;
+    size_t tab_cap = 0;
+    // workspace for `rows` tokens of a step
+    size_t rows = 0, want_cap = 0;
+    DevBuf<float> x, h, y, proj, la, u, go, qa, ol, gu, act, eo, sh_gu, sh_act, sh_o, route_w, sgate, hf, logits;
+    DevBuf<int> route_sel, pair_row, pair_of, grp_off;
+    PinnedBuf<float> h_logits;
+    // bf16 tensor-core path: hi/lo split of a GEMM's activations
+    DevBuf<uint16_t> xhi, xlo;
+    DevBuf<float> gemm_out;
+};
+
+void layered_build(LayeredModel& m, const fl_layer_desc* layers);
+void layered_put_tensor(LayeredModel& m, const char* name, int dtype, const int64_t* shape, int rank, const void* host);
+void layered_random_init(LayeredModel& m, uint64_t seed, float stdv);
+void layered_finalize(LayeredModel& m);
+
+}  // namespace fl
+
+struct fl_cache;
+namespace fl {
+void layered_cache_create(fl_cache& c, int max_slots, int max_seq, int pool_tokens);
+// one step of a mixed batch; logits of the wanted rows land in c.ly->h_logits (host, pinned) after the stream is synchronised
+void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, const uint32_t* ids, const int* want, int n_want);
+void layered_slot_reset(fl_cache& c, int slot);
+void layered_cache_reset(fl_cache& c);
+}  // namespace fl

@@ -1,0 +1,479 @@
+// Kernels of the layered decoder (sm_100a): residual / norm glue, the exact-f32 GEMM, gated linear attention (decay, scan, head
+// norm + gate), latent attention over the paged latent cache (append + rotary, absorbed-query attention), the clamped GLU
+// feed-forward and the mixture-of-experts router / row lists / combine.  Every mechanism takes its sizes and constants as
+// arguments.  Residual stream, norms, softmax, routers, decays and the recurrent state are f32 throughout; a row's result never
+// depends on which other rows share the launch (fixed summation order per output element).
+#pragma once
+#include <math.h>
+
+#include "common.cuh"
+
+namespace fl {
+
+// ---- per-step integer tables (one upload per step) -------------------------------------------------------------------------
+struct StepTab {
+    const int* tok;         // [T] token id of every row
+    const int* row_seq;     // [T] index of the row's sequence inside this step
+    const int* row_pos;     // [T] position of the row inside its sequence
+    const int* seq_row0;    // [n + 1] first row of every sequence
+    const int* seq_slot;    // [n] cache slot
+    const int* seq_pos0;    // [n] tokens the slot held before this step
+    const int* want;        // [n_want] rows whose logits are asked for
+    int T, n, n_want;
+};
+
+// cache element: float (exact mode) or bf16 bit pattern
+__device__ __forceinline__ float ld_c(const float* p) { return *p; }
+__device__ __forceinline__ float ld_c(const uint16_t* p) { return __uint_as_float((uint32_t)(*p) << 16); }
+__device__ __forceinline__ void st_c(float* p, float v) { *p = v; }
+__device__ __forceinline__ void st_c(uint16_t* p, float v) { *p = f32_to_bf16_rne(v); }
+
+__device__ __forceinline__ float block_sum(float v, float* red) {      // red: >= 33 floats of shared memory; all threads get the sum
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
+
+// ---- embedding + first norm ------------------------------------------------------------------------------------------------
+// x[row] = embed[tok[row]];  h[row] = x / sqrt(mean x^2 + eps) * (1 + w)
+static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, const int* __restrict__ tok, int W, const float* __restrict__ nw,
+                                            float eps, float* __restrict__ x, float* __restrict__ h) {
+    __shared__ float red[33];
+    const int row = blockIdx.x;
+    const uint16_t* e = embed + (size_t)tok[row] * W;
+    float* xr = x + (size_t)row * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = __uint_as_float((uint32_t)e[c] << 16);
+        xr[c] = v;
+        ss += v * v;
+    }
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    float* hr = h + (size_t)row * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = xr[c] * r * (1.f + nw[c]);
+}
+
+// x[row] += norm(y[row]; wb);  then, if wnext, h[row] = norm(x[row]; wnext)      (norm: weight stored around zero)
+static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
+                                           const float* __restrict__ wnext, float eps, int W, float* __restrict__ h) {
+    __shared__ float red[33];
+    const int row = blockIdx.x;
+    const float* yr = y + (size_t)row * W;
+    float* xr = x + (size_t)row * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) ss += yr[c] * yr[c];
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    float s2 = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = xr[c] + yr[c] * r * (1.f + wb[c]);
+        xr[c] = v;
+        s2 += v * v;
+    }
+    if (wnext == nullptr) return;
+    const float r2 = 1.f / sqrtf(block_sum(s2, red) / (float)W + eps);
+    float* hr = h + (size_t)row * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = xr[c] * r2 * (1.f + wnext[c]);
+}
+
+// hf[i] = norm(x[want[i]]; w): the rows that go on to the vocabulary projection
+static __global__ void ly_final_norm_kernel(const float* __restrict__ x, const int* __restrict__ want, const float* __restrict__ w, float eps, int W,
+                                            float* __restrict__ hf) {
+    __shared__ float red[33];
+    const float* xr = x + (size_t)want[blockIdx.x] * W;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) ss += xr[c] * xr[c];
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
+    float* hr = hf + (size_t)blockIdx.x * W;
+    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = xr[c] * r * (1.f + w[c]);
+}
+
+// ---- exact GEMM: Y[p, n] = sum_k A[row(p), k] * W[n, k]   (A f32, W bf16 bit patterns, f32 FMA in ascending k) ----------------------
+// Strided groups (blockIdx.z): group g uses A + g*a_gs, W + g*w_gs, Y + g*y_gs and the rows p in [grp_off[g], grp_off[g+1])
+// (grp_off == nullptr: rows [0, R) for every group).  a_idx gathers A rows (row(p) = a_idx[p]).
+struct LyGemm {
+    const float* A; long long a_gs; int lda; const int* a_idx;
+    const uint16_t* W; long long w_gs; int N, K;
+    float* Y; long long y_gs; int ldy;
+    const int* grp_off; int R;
+};
+constexpr int kLyBM = 64, kLyBN = 64, kLyBK = 16;
+
+static __global__ void __launch_bounds__(256) ly_gemm_kernel(LyGemm g) {
+    __shared__ float As[kLyBK][kLyBM + 4];
+    __shared__ float Ws[kLyBK][kLyBN + 4];
+    const int grp = blockIdx.z;
+    int p_lo = 0, p_hi = g.R;
+    if (g.grp_off != nullptr) { p_lo = g.grp_off[grp]; p_hi = g.grp_off[grp + 1]; }
+    const int p0 = p_lo + blockIdx.y * kLyBM;
+    if (p0 >= p_hi) return;
+    const int n0 = blockIdx.x * kLyBN;
+    const float* A = g.A + (size_t)grp * g.a_gs;
+    const uint16_t* Wm = g.W + (size_t)grp * g.w_gs;
+    float* Y = g.Y + (size_t)grp * g.y_gs;
+    const int tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int lr = tid >> 2, lk = (tid & 3) * 4;            // loader: row / first k of this thread's 4 elements
+    const int ap = p0 + lr;
+    const float* arow = nullptr;
+    if (ap < p_hi) arow = A + (size_t)(g.a_idx ? g.a_idx[ap] : ap) * g.lda;
+    const uint16_t* wrow = (n0 + lr < g.N) ? Wm + (size_t)(n0 + lr) * g.K : nullptr;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < g.K; k0 += kLyBK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i;
+            As[lk + i][lr] = (arow != nullptr && k < g.K) ? arow[k] : 0.f;
+            Ws[lk + i][lr] = (wrow != nullptr && k < g.K) ? __uint_as_float((uint32_t)wrow[k] << 16) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kLyBK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[kk][ty * 4 + i]; b[i] = Ws[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = p0 + ty * 4 + i;
+        if (p >= p_hi) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < g.N) Y[(size_t)p * g.ldy + n] = acc[i][j];
+        }
+    }
+}
+
+// ---- gated linear attention ------------------------------------------------------------------------------------------------
+// la[row, j] = log(sigmoid(a2[j, :] . a[row, :] + b[j])) / tau     (j over heads * dim key channels; a = the rank-r bottleneck)
+static __global__ void ly_gla_decay_kernel(const float* __restrict__ proj, int ldp, int off_a, int rank, const float* __restrict__ a2,
+                                           const float* __restrict__ a2b, int HD, float inv_tau, float* __restrict__ la) {
+    extern __shared__ float s_a[];
+    const int row = blockIdx.x;
+    for (int r = threadIdx.x; r < rank; r += blockDim.x) s_a[r] = proj[(size_t)row * ldp + off_a + r];
+    __syncthreads();
+    for (int j = threadIdx.x; j < HD; j += blockDim.x) {
+        float z = a2b[j];
+        const float* w = a2 + (size_t)j * rank;
+        for (int r = 0; r < rank; ++r) z = fmaf(w[r], s_a[r], z);
+        // log sigmoid(z) = -(max(-z, 0) + log1p(exp(-|z|)))
+        la[(size_t)row * HD + j] = -(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))) * inv_tau;
+    }
+}
+
+struct GlaArgs {
+    const float* proj; int ldp, off_q, off_k, off_v;
+    const float* la;            // [T, H*D] log decay
+    float* o;                   // [T, H*Dv]
+    float* state;               // [slots][H][D][Dv]
+    const int *seq_row0, *seq_slot, *seq_pos0;
+    int H, D, Dv;
+    float qscale;
+};
+constexpr int kGlaVS = 32, kGlaDG = 8;        // value columns per block, key-channel groups per block
+
+// The recurrence itself, token by token: S <- diag(alpha_t) S + k_t v_t^T, o_t = S^T (q_t * qscale).  One block per
+// (sequence, head, 32 value columns): columns of S never interact, so the state is cut along vdim.  Thread (vcol, dg) keeps rows
+// dg, dg + 8, ... of its column in registers.  The order of operations per token does not depend on how a prompt was cut.
+template <int RPT>
+static __global__ void __launch_bounds__(kGlaVS * kGlaDG) ly_gla_scan_kernel(GlaArgs a) {
+    extern __shared__ float sm[];
+    const int D = a.D, Dv = a.Dv;
+    float* sq = sm;                     // [2][D]
+    float* sk = sq + 2 * D;             // [2][D]
+    float* sa = sk + 2 * D;             // [2][D]
+    float* sv = sa + 2 * D;             // [2][32]
+    float* red = sv + 2 * kGlaVS;       // [2][8][32]
+    const int seq = blockIdx.x, hd = blockIdx.y, v0 = blockIdx.z * kGlaVS;
+    const int tid = threadIdx.x, vc = tid & 31, dg = tid >> 5;
+    const int r0 = a.seq_row0[seq], r1 = a.seq_row0[seq + 1];
+    const bool vok = v0 + vc < Dv;
+    float* st = a.state + (((size_t)a.seq_slot[seq] * a.H + hd) * D) * Dv + v0 + vc;
+    float s[RPT];
+    const bool fresh = a.seq_pos0[seq] == 0;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int d = dg + kGlaDG * i;
+        s[i] = (!fresh && vok && d < D) ? st[(size_t)d * Dv] : 0.f;
+    }
+    int b = 0;
+    for (int row = r0; row <= r1; ++row, b ^= 1) {
+        if (row < r1) {
+            const float* pr = a.proj + (size_t)row * a.ldp;
+            for (int i = tid; i < D; i += blockDim.x) {
+                sq[b * D + i] = pr[a.off_q + hd * D + i] * a.qscale;
+                sk[b * D + i] = pr[a.off_k + hd * D + i];
+                sa[b * D + i] = expf(a.la[(size_t)row * a.H * D + hd * D + i]);
+            }
+            if (tid < kGlaVS) sv[b * kGlaVS + tid] = (v0 + tid < Dv) ? pr[a.off_v + hd * Dv + v0 + tid] : 0.f;
+        }
+        __syncthreads();
+        if (row > r0 && dg == 0 && vok) {          // finish the previous token: add the 8 partial sums in a fixed order
+            const float* rp = red + (b ^ 1) * kGlaDG * kGlaVS;
+            float t = 0.f;
+#pragma unroll
+            for (int g = 0; g < kGlaDG; ++g) t += rp[g * kGlaVS + vc];
+            a.o[(size_t)(row - 1) * a.H * Dv + hd * Dv + v0 + vc] = t;
+        }
+        if (row < r1) {
+            const float v = sv[b * kGlaVS + vc];
+            float acc = 0.f;
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) {
+                const int d = dg + kGlaDG * i;
+                if (d < D) {
+                    s[i] = fmaf(s[i], sa[b * D + d], sk[b * D + d] * v);
+                    acc = fmaf(s[i], sq[b * D + d], acc);
+                }
+            }
+            red[(b * kGlaDG + dg) * kGlaVS + vc] = acc;
+        }
+    }
+    if (vok) {
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            const int d = dg + kGlaDG * i;
+            if (d < D) st[(size_t)d * Dv] = s[i];
+        }
+    }
+}
+
+// u[row, h, :] = o[row, h, :] / sqrt(mean o^2 + eps) * w[:] * silu(g[row, h, :])     (one warp per (row, head))
+static __global__ void ly_gla_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, int ldp, int off_g, const float* __restrict__ w,
+                                         float eps, int T, int H, int Dv, float* __restrict__ u) {
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (item >= T * H) return;
+    const int row = item / H, hd = item % H;
+    const float* op = o + (size_t)row * H * Dv + hd * Dv;
+    float ss = 0.f;
+    for (int c = lane; c < Dv; c += 32) ss += op[c] * op[c];
+    const float r = 1.f / sqrtf(warp_sum(ss) / (float)Dv + eps);
+    const float* gp = proj + (size_t)row * ldp + off_g + hd * Dv;
+    float* up = u + (size_t)row * H * Dv + hd * Dv;
+    for (int c = lane; c < Dv; c += 32) {
+        const float g = gp[c];
+        up[c] = op[c] * r * w[c] * (g * sigmoidf_(g));
+    }
+}
+
+// ---- latent attention ------------------------------------------------------------------------------------------------------
+struct LatentAppendArgs {
+    float* proj; int ldp, off_q, off_dkv;       // off_dkv < 0: the layer reads another layer's cache (queries are still rotated)
+    const float* dkv_norm; float eps;
+    void* pool;                                  // [pages][64][C + R]
+    const int* page_table; int pps;
+    const int *row_seq, *row_pos, *seq_slot;
+    const float *cosb, *sinb;                    // [max_seq][rdims / 2], already multiplied by the YaRN magnitude
+    int H, D, R, C, rdims;
+};
+// Per row: the latent (RMS-normed, plain weight) and the rotated shared key part go into the row's cache page; the rotated part of
+// every head's query is turned in place.  Pairs (2i, 2i+1) of the first rdims channels turn by pos * f_i; the rest pass through.
+template <typename CT>
+static __global__ void ly_latent_append_kernel(LatentAppendArgs a) {
+    __shared__ float red[33];
+    const int row = blockIdx.x, pos = a.row_pos[row];
+    float* pr = a.proj + (size_t)row * a.ldp;
+    const float* cs = a.cosb + (size_t)pos * (a.rdims / 2);
+    const float* sn = a.sinb + (size_t)pos * (a.rdims / 2);
+    for (int i = threadIdx.x; i < a.H * (a.rdims / 2); i += blockDim.x) {
+        const int hd = i / (a.rdims / 2), pi = i % (a.rdims / 2);
+        float* q = pr + a.off_q + hd * (a.D + a.R) + a.D + 2 * pi;
+        const float u = q[0], v = q[1];
+        q[0] = u * cs[pi] - v * sn[pi];
+        q[1] = v * cs[pi] + u * sn[pi];
+    }
+    if (a.off_dkv < 0) return;
+    const int slot = a.seq_slot[a.row_seq[row]];
+    const int page = a.page_table[(size_t)slot * a.pps + pos / kKvPage];
+    CT* dst = (CT*)a.pool + ((size_t)page * kKvPage + pos % kKvPage) * (a.C + a.R);
+    const float* ckv = pr + a.off_dkv;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < a.C; c += blockDim.x) ss += ckv[c] * ckv[c];
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)a.C + a.eps);
+    for (int c = threadIdx.x; c < a.C; c += blockDim.x) st_c(dst + c, ckv[c] * r * a.dkv_norm[c]);
+    for (int i = threadIdx.x; i < a.R; i += blockDim.x) {
+        float val;
+        if (i < a.rdims) {
+            const int pi = i >> 1;
+            const float u = ckv[a.C + 2 * pi], v = ckv[a.C + 2 * pi + 1];
+            val = (i & 1) ? v * cs[pi] + u * sn[pi] : u * cs[pi] - v * sn[pi];
+        } else {
+            val = ckv[a.C + i];
+        }
+        st_c(dst + a.C + i, val);
+    }
+}
+
+struct LatentAttnArgs {
+    const float* qa;            // [T, H, C] queries with W_uk absorbed
+    const float* proj; int ldp, off_q;          // rotated query part lives at proj[row, off_q + h (D + R) + D ...]
+    const void* pool; const int* page_table; int pps;
+    const int *row_seq, *row_pos, *seq_slot;
+    float* ol;                  // [T, H, C] softmax-weighted sum of latents
+    int H, D, R, C, window;
+    float scale;
+};
+constexpr int kLatWarps = 4;
+// One block per (row, head).  score_j = (q~ . c_j + q_rot . k_rot_j) * scale over the keys j the window admits (0 <= pos - j <
+// window), softmax in f32, out = sum_j p_j c_j.  Warp w folds keys j0 + w, j0 + w + 4, ... into an online softmax (lanes own
+// channels); the four partial results are merged at the end.  Which warp takes which key depends on the position alone.
+template <typename CT, int CPL>
+static __global__ void __launch_bounds__(kLatWarps * 32) ly_latent_attn_kernel(LatentAttnArgs a) {
+    extern __shared__ float sm[];               // [kLatWarps][C] accumulators, then [kLatWarps][2] (max, sum)
+    constexpr int RPL = 4;                      // rotated channels per lane (R <= 128)
+    const int row = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int C = a.C, R = a.R, E = C + R;
+    const int pos = a.row_pos[row], slot = a.seq_slot[a.row_seq[row]];
+    const int j0 = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    float q[CPL], qr[RPL], acc[CPL];
+    const float* qap = a.qa + ((size_t)row * a.H + hd) * C;
+    const float* qrp = a.proj + (size_t)row * a.ldp + a.off_q + hd * (a.D + R) + a.D;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) { const int c = lane + 32 * i; q[i] = c < C ? qap[c] : 0.f; acc[i] = 0.f; }
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) { const int c = lane + 32 * i; qr[i] = c < R ? qrp[c] : 0.f; }
+    float m = -INFINITY, l = 0.f;
+    const int* pt = a.page_table + (size_t)slot * a.pps;
+    for (int j = j0 + wid; j <= pos; j += kLatWarps) {
+        const CT* kp = (const CT*)a.pool + ((size_t)pt[j / kKvPage] * kKvPage + j % kKvPage) * E;
+        float lat[CPL], dot = 0.f;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) { const int c = lane + 32 * i; lat[i] = c < C ? ld_c(kp + c) : 0.f; dot = fmaf(q[i], lat[i], dot); }
+#pragma unroll
+        for (int i = 0; i < RPL; ++i) { const int c = lane + 32 * i; if (c < R) dot = fmaf(qr[i], ld_c(kp + C + c), dot); }
+        const float s = warp_sum(dot) * a.scale;
+        const float mn = fmaxf(m, s), corr = expf(m - mn), p = expf(s - mn);
+        l = l * corr + p;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) acc[i] = acc[i] * corr + p * lat[i];
+        m = mn;
+    }
+    float* sacc = sm;
+    float* sml = sm + kLatWarps * C;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) { const int c = lane + 32 * i; if (c < C) sacc[wid * C + c] = acc[i]; }
+    if (lane == 0) { sml[2 * wid] = m; sml[2 * wid + 1] = l; }
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kLatWarps; ++w) M = fmaxf(M, sml[2 * w]);
+    float f[kLatWarps], Lsum = 0.f;
+#pragma unroll
+    for (int w = 0; w < kLatWarps; ++w) { f[w] = expf(sml[2 * w] - M); Lsum += sml[2 * w + 1] * f[w]; }
+    const float inv = 1.f / Lsum;
+    float* op = a.ol + ((size_t)row * a.H + hd) * C;
+    for (int c = threadIdx.x; c < C; c += blockDim.x) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < kLatWarps; ++w) t += sacc[w * C + c] * f[w];
+        op[c] = t * inv;
+    }
+}
+
+// ---- feed-forward ----------------------------------------------------------------------------------------------------------
+// act[p, f] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[p, f], limit),  u = clamp(gu[p, F + f], -limit, limit);  p < *count
+static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float limit, const int* __restrict__ count, int rows, float* __restrict__ act) {
+    const int n = count ? *count : rows;
+    const size_t total = (size_t)n * F;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t p = i / F, f = i - p * F;
+        const float g = fminf(gu[p * 2 * F + f], limit);
+        const float u = fminf(fmaxf(gu[p * 2 * F + F + f], -limit), limit);
+        act[i] = g * sigmoidf_(1.702f * g) * (u + 1.f);
+    }
+}
+
+// Router: z = Wr h (f32), s = softmax(z) over all experts, the `top` largest (lower index first among equals), weights s / (sum + 1e-20).
+// Also the shared expert's gate sigmoid(w_sg . h).  One block per row, one warp per expert in turn.
+static __global__ void ly_router_kernel(const float* __restrict__ h, int W, const float* __restrict__ wr, int E, int top, const float* __restrict__ wsg,
+                                        int* __restrict__ sel, float* __restrict__ wt, float* __restrict__ sgate) {
+    extern __shared__ float z[];                 // [E]
+    const int row = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const float* hr = h + (size_t)row * W;
+    for (int e = wid; e <= E; e += nw) {
+        if (e == E && wsg == nullptr) break;
+        const float* w = e < E ? wr + (size_t)e * W : wsg;
+        float d = 0.f;
+        for (int c = lane; c < W; c += 32) d = fmaf(w[c], hr[c], d);
+        d = warp_sum(d);
+        if (lane == 0) {
+            if (e < E) z[e] = d; else sgate[row] = sigmoidf_(d);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float mx = -INFINITY;
+        for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[e]);
+        float sum = 0.f;
+        for (int e = 0; e < E; ++e) { z[e] = expf(z[e] - mx); sum += z[e]; }
+        const float inv = 1.f / sum;
+        float psum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            float bv = -1.f;
+            for (int e = 0; e < E; ++e)
+                if (z[e] > bv) { bv = z[e]; best = e; }
+            sel[row * top + k] = best;
+            wt[row * top + k] = bv * inv;
+            psum += bv * inv;
+            z[best] = -2.f;
+        }
+        const float pinv = 1.f / (psum + 1e-20f);
+        for (int k = 0; k < top; ++k) wt[row * top + k] *= pinv;
+    }
+}
+
+// Row lists per expert, in ascending (row, pick) order: grp_off[E + 1], pair_row[p] = source row, pair_of[row * top + k] = p.
+// One block; thread e places expert e's pairs (stable), so the lists do not depend on timing.
+static __global__ void ly_moe_lists_kernel(const int* __restrict__ sel, int T, int top, int E, int* __restrict__ grp_off, int* __restrict__ pair_row,
+                                           int* __restrict__ pair_of) {
+    extern __shared__ int cnt[];                 // [E + 1]
+    const int n = T * top;
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int c = 0;
+        for (int i = 0; i < n; ++i) c += sel[i] == e;
+        cnt[e] = c;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int run = 0;
+        for (int e = 0; e < E; ++e) { const int c = cnt[e]; cnt[e] = run; grp_off[e] = run; run += c; }
+        grp_off[E] = run;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+        int p = cnt[e];
+        for (int i = 0; i < n; ++i)
+            if (sel[i] == e) { pair_row[p] = i / top; pair_of[i] = p; ++p; }
+    }
+}
+
+// y[row, c] = sum_k wt[row, k] * eo[pair_of[row, k], c]  (pick order)  + sgate[row] * sh[row, c]
+static __global__ void ly_moe_combine_kernel(const float* __restrict__ eo, const int* __restrict__ pair_of, const float* __restrict__ wt, int top,
+                                             const float* __restrict__ sh, const float* __restrict__ sgate, int W, float* __restrict__ y) {
+    const int row = blockIdx.y;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < W; c += gridDim.x * blockDim.x) {
+        float t = 0.f;
+        for (int k = 0; k < top; ++k) t = fmaf(wt[row * top + k], eo[(size_t)pair_of[row * top + k] * W + c], t);
+        if (sh != nullptr) t = fmaf(sgate[row], sh[(size_t)row * W + c], t);
+        y[(size_t)row * W + c] = t;
+    }
+}
+
+}  // namespace fl

@@ -10,6 +10,7 @@
 #include "bert_model.cuh"
 #include "decode_persistent.cuh"
 #include "gemv.cuh"
+#include "layered_model.cuh"
 #include "runtime.cuh"
 
 namespace fl {
@@ -118,10 +119,13 @@ struct GraphEntry {
 struct fl_model {
     std::shared_ptr<fl::Weights> w;       // causal LMs
     std::shared_ptr<fl::BertModel> bert;  // BERT-family encoder (arch == FL_ARCH_BERT)
+    std::shared_ptr<fl::LayeredModel> lay;   // layered decoder (fl_model_create_layered)
 };
 
 struct fl_cache {
     std::shared_ptr<fl::Weights> w;
+    std::shared_ptr<fl::LayeredModel> lm;  // layered decoder: the cache below is then `ly` (pooled pages + state slots) and only
+    std::unique_ptr<fl::LayeredCache> ly;  //   stream / max_batch / max_seq / pages_per_seq / slot_len / poisoned of this struct are used
     cudaStream_t stream = nullptr;
     int max_batch = 0, max_seq = 0, pages_per_seq = 0, nsplit = 1;
     int kv_len = 0;                       // host mirror of StepState.kv_base (same for every sequence; the uniform calls)

@@ -100,6 +100,7 @@ struct DevBuf {
     DevBuf() = default;
     DevBuf(const DevBuf&) = delete;
     DevBuf& operator=(const DevBuf&) = delete;
+    DevBuf(DevBuf&& o) noexcept : p(o.p), n(o.n) { o.p = nullptr; o.n = 0; }      // lets containers of buffers grow
     ~DevBuf() { release(); }
     void alloc(size_t count, bool zero = false) {
         release();

@@ -31,14 +31,20 @@ from ._lib import FastllmError, FlConfig
 class DeviceModel:
     """fl_model*: device weights (shared between clones)."""
 
-    def __init__(self, cfg: FlConfig, device: int = 0, _handle=None):
+    def __init__(self, cfg, device: int = 0, _handle=None, layers=None):
+        """cfg: FlConfig, or FlStackConfig + `layers` (a ctypes array of FlLayerDesc) for a layered model."""
         _lib.init(device)
         self.lib = _lib.load()
         self.cfg = cfg
+        self.layers = layers
         self.device = device
+        self.vocab = cfg.vocab if isinstance(cfg, _lib.FlStackConfig) else cfg.vocab_size
         if _handle is None:
             h = C.c_void_p()
-            _lib.check(self.lib.fl_model_create(C.byref(cfg), C.byref(h)))
+            if layers is not None:
+                _lib.check(self.lib.fl_model_create_layered(C.byref(cfg), layers, C.byref(h)))
+            else:
+                _lib.check(self.lib.fl_model_create(C.byref(cfg), C.byref(h)))
             self.h = h
         else:
             self.h = _handle
@@ -65,7 +71,7 @@ class DeviceModel:
     def clone(self) -> "DeviceModel":
         h = C.c_void_p()
         _lib.check(self.lib.fl_model_clone(self.h, C.byref(h)))
-        return DeviceModel(self.cfg, self.device, _handle=h)
+        return DeviceModel(self.cfg, self.device, _handle=h, layers=self.layers)
 
     def streamed_bytes(self) -> int:
         n = C.c_uint64()
@@ -84,13 +90,51 @@ class DeviceModel:
 class DeviceCache:
     """fl_cache*: paged KV cache + per-cache stream/workspaces."""
 
-    def __init__(self, model: DeviceModel, max_batch: int, max_seq: int):
+    def __init__(self, model: DeviceModel, max_batch: int, max_seq: int, pool_tokens: int | None = None):
+        """pool_tokens (layered models): the cache's pages are a pool of that many tokens shared by the max_batch sequence slots,
+        handed out as sequences grow and given back by slot_reset; None = room for max_batch x max_seq tokens."""
         self.model, self.lib = model, model.lib
         self.max_batch, self.max_seq = max_batch, max_seq
-        self.vocab = model.cfg.vocab_size
+        self.vocab = model.vocab
         h = C.c_void_p()
-        _lib.check(self.lib.fl_cache_create(model.h, max_batch, max_seq, C.byref(h)))
+        if pool_tokens is None:
+            _lib.check(self.lib.fl_cache_create(model.h, max_batch, max_seq, C.byref(h)))
+        else:
+            _lib.check(self.lib.fl_cache_create_pooled(model.h, max_batch, max_seq, pool_tokens, C.byref(h)))
         self.h = h
+
+    def forward_ragged(self, slots, token_lists, want=None) -> np.ndarray:
+        """One step of a mixed batch (layered models): sequence i lives in slot slots[i] and is fed token_lists[i] (a portion of its
+        prompt, or one decoded token) after what the slot already holds.  want: per sequence the places inside its portion whose
+        logits are asked for (None = the last token of every portion).  -> f32 [sum of wanted places, vocab], sequence-major."""
+        n = len(slots)
+        counts = np.asarray([len(t) for t in token_lists], dtype=np.int32)
+        if len(token_lists) != n or (counts < 1).any():
+            raise FastllmError(-1, "every sequence of a step brings at least one token")
+        ids = np.ascontiguousarray(np.concatenate([np.asarray(t, dtype=np.uint32).reshape(-1) for t in token_lists]))
+        starts = np.concatenate([[0], np.cumsum(counts)])
+        if want is None:
+            rows = [int(starts[i + 1]) - 1 for i in range(n)]
+        else:
+            rows = []
+            for i, places in enumerate(want):
+                for p in places:
+                    if not 0 <= p < counts[i]:
+                        raise FastllmError(-1, "a wanted place lies outside its portion")
+                    rows.append(int(starts[i]) + int(p))
+        rows = np.asarray(rows, dtype=np.int32)
+        sl = np.ascontiguousarray(slots, dtype=np.int32)
+        out = np.empty((len(rows), self.vocab), dtype=np.float32)
+        _lib.check(self.lib.fl_forward_ragged(self.model.h, self.h, sl.ctypes.data_as(C.c_void_p), counts.ctypes.data_as(C.c_void_p), n,
+                                              ids.ctypes.data_as(C.c_void_p), rows.ctypes.data_as(C.c_void_p), len(rows),
+                                              out.ctypes.data_as(C.c_void_p)))
+        return out
+
+    def pool_stats(self):
+        """-> (pages of the pool, pages free)"""
+        a, b = C.c_int(), C.c_int()
+        _lib.check(self.lib.fl_cache_pool_stats(self.h, C.byref(a), C.byref(b)))
+        return a.value, b.value
 
     def reset(self):
         _lib.check(self.lib.fl_cache_reset(self.h))
@@ -430,6 +474,161 @@ class MixtralWithConfig(MistralWithConfig):
         return _fl_config("mixtral", cf, 32768, cf.sliding_window if cf.sliding_window is not None else 4096, False)
 
 
+class NifunexCache(_OffsetCache):
+    """Cache handle of the layered decoder: owns the device cache (latent pages + recurrent-state slots), created on first use."""
+
+    def __init__(self):
+        super().__init__()
+        self.inner: DeviceCache | None = None
+
+
+def nifunex_layer_descs(config: dict, decay_ranks: dict):
+    """config.json of the layered decoder -> ctypes array of FlLayerDesc.  decay_ranks: layer index -> rows of that layer's decay
+    bottleneck (the one size the file does not spell out; it is the first dimension of 'l<i>.mix.a1')."""
+    layers = config["layers"]
+    arr = (_lib.FlLayerDesc * len(layers))()
+    for i, l in enumerate(layers):
+        d, m = arr[i], l["mixer"]
+        if l["type"] not in _lib.FL_MIXER:
+            raise FastllmError(-1, f"layer {i}: unknown mixer type {l['type']!r}")
+        d.mixer = _lib.FL_MIXER[l["type"]]
+        d.heads, d.dim, d.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
+        d.kv_from = -1
+        if l["type"] == "gla":
+            d.tau = float(m["tau"])
+            if i not in decay_ranks:
+                raise FastllmError(-1, f"layer {i}: the decay bottleneck's size is unknown (no 'l{i}.mix.a1' tensor and no decay_rank)")
+            d.decay_rank = int(decay_ranks[i])
+        else:
+            d.rot_dim, d.kv_rank = int(m["rot_dim"]), int(m["kv_rank"])
+            d.kv_from = int(m["kv_from"]) if m.get("kv_from") is not None else -1
+            d.window = int((m.get("mask") or {}).get("size") or 0)
+            rot = m.get("rot") or {}
+            d.rot_dims = int(rot.get("dims", d.rot_dim))
+            d.rot_base = float(rot.get("base", 10000.0))
+            d.scale = float(m["scale"])
+            sc = rot.get("scaling")
+            if sc:
+                d.yarn_factor, d.yarn_original = float(sc["factor"]), float(sc["original"])
+                d.yarn_fast, d.yarn_slow = float(sc["fast"]), float(sc["slow"])
+        mlp = l.get("mlp")
+        if not mlp:
+            d.ffn = _lib.FL_FFN["none"]
+        elif mlp["kind"] == "dense":
+            d.ffn, d.ff, d.limit = _lib.FL_FFN["dense"], int(mlp["ff"]), float(mlp["limit"])
+        elif mlp["kind"] == "moe":
+            d.ffn, d.ff, d.limit = _lib.FL_FFN["moe"], int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
+            d.experts, d.top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
+            if mlp.get("shared"):
+                d.shared_ff, d.shared_limit = int(mlp["shared"]["ff"]), float(mlp["shared"]["limit"])
+        else:
+            raise FastllmError(-1, f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+    return arr
+
+
+class NifunexWithConfig(_CausalBase):
+    """The layered decoder (no reference path): gated-linear-attention and windowed latent-attention layers, dense / MoE
+    feed-forward, norms before and after every sublayer.  `config` is the parsed config.json (a dict: vocab, width, norm.eps and
+    one entry per layer).  Positions are the caller's, as for Llama; the device cache hands out pages on demand and keeps a
+    recurrent-state slot per sequence."""
+    arch, family, architectures = "nifunex", "Nifunex", ("Nifunex",)
+    position_per_call = False
+    MAX_BATCH = 1
+    POOL_TOKENS = None          # None: room for MAX_BATCH x capacity tokens
+
+    def __init__(self, dev: DeviceModel, cfg, config: dict):
+        super().__init__(dev, cfg)
+        self.config = config
+
+    @classmethod
+    def initialize_model(cls, config: dict, tensors, dtype="bf16", device: int = 0, *, random_seed=None, std: float = 0.02, decay_rank=None):
+        """tensors: dict or iterable of (name, array) (f32 / f16 / uint16 bf16 bits), or None for synthetic weights (then
+        decay_rank gives the decay bottleneck's rows).  dtype "bf16": the serving precision; "f32": every product and the cache in
+        true 32-bit."""
+        if dtype not in ("bf16", "bfloat16", "f32", "float32"):
+            raise FastllmError(-1, f"unsupported dtype {dtype!r}")
+        items = None
+        ranks = {}
+        if tensors is not None:
+            items = list(tensors.items() if hasattr(tensors, "items") else tensors)
+            for name, arr in items:
+                if name.endswith(".mix.a1") and name[0] == "l":
+                    ranks[int(name[1:name.index(".")])] = int(np.asarray(arr).shape[0])
+        else:
+            ranks = {i: int(decay_rank or 16) for i, l in enumerate(config["layers"]) if l["type"] == "gla"}
+        sc = _lib.FlStackConfig()
+        sc.arch = _lib.FL_ARCH["nifunex"]
+        sc.vocab, sc.width, sc.n_layers = int(config["vocab"]), int(config["width"]), len(config["layers"])
+        sc.norm_eps = float(config["norm"]["eps"])
+        sc.compute_dtype = _lib.FL_DTYPE_F32 if dtype in ("f32", "float32") else _lib.FL_DTYPE_BF16
+        dev = DeviceModel(sc, device, layers=nifunex_layer_descs(config, ranks))
+        if items is None:
+            dev.random_init(0 if random_seed is None else random_seed, std)
+        else:
+            for name, arr in items:
+                a = np.asarray(arr)
+                if a.dtype.kind in "iu" and a.dtype != np.uint16:
+                    continue            # integer tables: this design reads none
+                dev.put_tensor(name, a)
+        dev.finalize()
+        self = cls(dev, sc, config)
+        return self, cls.initialize_cache(device, dtype)
+
+    @staticmethod
+    def initialize_cache(device=0, dtype="bf16") -> NifunexCache:
+        return NifunexCache()
+
+    def _capacity(self) -> int:
+        return self.KV_CAPACITY
+
+    def new_device_cache(self, max_batch: int | None = None, max_seq: int | None = None, pool_tokens: int | None = None) -> DeviceCache:
+        return DeviceCache(self.dev, max_batch or self.MAX_BATCH, max_seq or self._capacity(), pool_tokens if pool_tokens is not None else self.POOL_TOKENS)
+
+    def forward(self, input: np.ndarray, pos: int, cache: NifunexCache) -> np.ndarray:
+        """[b, t] token ids at positions pos.. -> f32 [b, V] logits of the last position (pos must equal what the cache holds)."""
+        ids = np.asarray(input)
+        if ids.ndim != 2:
+            raise FastllmError(-1, f"input must be [batch, seq], got shape {ids.shape}")
+        if cache.inner is None:
+            cache.inner = self.new_device_cache(max(self.MAX_BATCH, ids.shape[0]))
+        return cache.inner.forward(ids, pos)
+
+    def clone(self) -> "NifunexWithConfig":
+        return NifunexWithConfig(self.dev.clone(), self.cfg, self.config)
+
+
+# every adapter, in the order the registry tries them (model_registry.rs:169-182 keeps the same kind of list)
+def registered_models():
+    return (LlamaWithConfig, MistralWithConfig, QwenWithConfig, MixtralWithConfig, NifunexWithConfig)
+
+
+def model_class_for(config: dict):
+    """The adapter whose supports_architecture accepts the config.json's `architectures` list (HF) or `architecture` name."""
+    names = list(config.get("architectures") or [])
+    if config.get("architecture"):
+        names.append(config["architecture"])
+    for cls in registered_models():
+        if any(cls.supports_architecture(n) for n in names):
+            return cls
+    raise FastllmError(-5, f"no registered model supports {names}")
+
+
+def load_model(model_dir: str, dtype: str = "bf16", device: int = 0):
+    """config.json + safetensors of a folder -> (adapter instance, cache handle), the class chosen by the registry."""
+    import os
+    from . import safetensors_io
+    with open(os.path.join(model_dir, "config.json")) as f:
+        config = json.load(f)
+    cls = model_class_for(config)
+    if cls is NifunexWithConfig:
+        return cls.initialize_model(config, safetensors_io.iter_tensors(model_dir, copy=True), dtype, device)
+    cf = ConfigFile(config["hidden_size"], config["intermediate_size"], config["vocab_size"], config["num_hidden_layers"],
+                    config["num_attention_heads"], config.get("num_key_value_heads"), config.get("rms_norm_eps", 1e-5),
+                    config.get("rope_theta"), config.get("max_position_embeddings"), config.get("sliding_window"),
+                    num_local_experts=config.get("num_local_experts", 0), num_experts_per_tok=config.get("num_experts_per_tok", 2))
+    return cls.initialize_model(cf, safetensors_io.iter_tensors(model_dir), dtype, device)
+
+
 class LogitsProcessor:
     """candle's LogitsProcessor as the reference builds it: LogitsProcessor::new(Default::default(), Some(temperature as f64),
     None) (mod.rs:157-158, 373-374).  Temperature < 1e-7 => arg-max (IEEE total order, LAST index among equal maxima);
@@ -569,7 +768,8 @@ class ContinuousBatcher:
 
     def __init__(self, model, max_batch: int = 8, eos_token_id: int | None = 2, cache=None):
         self.model, self.max_batch, self.eos_token_id = model, max_batch, eos_token_id
-        self.position_per_call = getattr(model, "arch", "llama") != "llama"      # the Mistral/Qwen2 adapters' offset rule
+        # the Mistral/Qwen2 adapters' offset rule (+1 per call); Llama and the layered decoder take true positions
+        self.position_per_call = getattr(model, "position_per_call", getattr(model, "arch", "llama") != "llama")
         self.cache = cache if cache is not None else DeviceCache(model.dev, max_batch, model._capacity())
         self.steps = 0          # ragged decode forwards issued (tests / stats)
 

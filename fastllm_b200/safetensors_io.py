@@ -18,7 +18,8 @@ import struct
 
 import numpy as np
 
-_DTYPES = {"F32": np.float32, "F16": np.float16, "BF16": np.uint16}     # bf16 travels as raw bit patterns (FL_DTYPE_BF16)
+_DTYPES = {"F32": np.float32, "F16": np.float16, "BF16": np.uint16,     # bf16 travels as raw bit patterns (FL_DTYPE_BF16)
+           "I32": np.int32, "I64": np.int64}                              # integer tables (handed on as they are)
 
 
 class SafetensorsFile:
@@ -75,13 +76,14 @@ def checkpoint_files(model_dir: str):
     return [os.path.join(model_dir, f) for f in sorted(set(wm.values()))]
 
 
-def iter_tensors(model_dir: str):
-    """Yields (name, array-over-the-mapping) for every tensor of the checkpoint; the array is valid until the next yield."""
+def iter_tensors(model_dir: str, copy: bool = False):
+    """Yields (name, array-over-the-mapping) for every tensor of the checkpoint; the array is valid until the next yield
+    (copy=True yields private copies, for callers that keep the list)."""
     for path in checkpoint_files(model_dir):
         sf = SafetensorsFile(path)
         try:
             for name in sf.names():
-                yield name, sf.get(name)
+                yield name, (np.array(sf.get(name)) if copy else sf.get(name))
         finally:
             sf.close()
 

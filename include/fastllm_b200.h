@@ -67,7 +67,9 @@ typedef enum fl_arch {
     FL_ARCH_MISTRAL = 1,   /* MistralForCausalLM        (models/mistral.rs) */
     FL_ARCH_QWEN2 = 2,     /* Qwen2ForCausalLM, qkv bias (models/qwen.rs)    */
     FL_ARCH_MIXTRAL = 3,   /* MixtralForCausalLM top-k MoE (no reference path; candle mixtral.rs) */
-    FL_ARCH_BERT = 4       /* BertModel encoder         (models/embeddings.rs) */
+    FL_ARCH_BERT = 4,      /* BertModel encoder         (models/embeddings.rs) */
+    FL_ARCH_NIFUNEX = 5    /* layered decoder described by fl_layer_desc (no reference path): gated-linear-attention and windowed
+                              latent-attention mixers, dense / mixture-of-experts feed-forward, a norm before and after each sublayer */
 } fl_arch;
 
 typedef enum fl_dtype { FL_DTYPE_F32 = 0, FL_DTYPE_BF16 = 1, FL_DTYPE_F16 = 2 } fl_dtype;
@@ -97,6 +99,54 @@ typedef struct fl_config {
     int32_t reserved[5];
 } fl_config;
 
+/* ---- layered models: every layer names its own mixer and feed-forward (no reference counterpart) ----------------------------
+ * A layer is  x += norm_b(mixer(norm_a(x)));  x += norm_d(ffn(norm_c(x)))  with RMS norms whose weight is stored around zero
+ * (x / sqrt(mean x^2 + eps) * (1 + w)).  Mixers:
+ *   FL_MIXER_GLA          gated linear attention: per head a [dim, vdim] f32 state S <- diag(alpha) S + k v^T, o = S^T q with a
+ *                         per-key-channel decay alpha = sigmoid(W_a2 W_a1 h + b)^(1/tau) through a rank-`decay_rank` bottleneck;
+ *                         o is RMS-normed per head, gated by silu(W_g h) and projected.  The state lives in a per-sequence slot.
+ *   FL_MIXER_LATENT_ATTN  attention over a shared compressed key/value: the cache holds per token a `kv_rank` latent (RMS-normed)
+ *                         and ONE rotated `rot_dim` key part; heads expand keys / values from the latent (W_uk, W_uv).  Interleaved
+ *                         rotary embedding with optional YaRN frequency scaling, sliding window (`window` keys, 0 = none), plain
+ *                         softmax with the given `scale`.  kv_from >= 0: the layer reads layer kv_from's cached latent instead of
+ *                         projecting its own.
+ * Feed-forward: y = W_down (g * sigmoid(1.702 g) * (u + 1)), g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit); dense, or
+ * `top` of `experts` such experts weighted by their renormalised softmax scores plus an optional always-on shared expert scaled by
+ * sigmoid(w_sg . h). */
+typedef enum fl_mixer_kind { FL_MIXER_GLA = 0, FL_MIXER_LATENT_ATTN = 1 } fl_mixer_kind;
+typedef enum fl_ffn_kind { FL_FFN_NONE = 0, FL_FFN_DENSE = 1, FL_FFN_MOE = 2 } fl_ffn_kind;
+
+typedef struct fl_layer_desc {
+    int32_t mixer;                     /* fl_mixer_kind */
+    int32_t heads, dim, vdim;          /* per head: query/key channels (unrotated part for latent attention), value channels */
+    int32_t decay_rank;                /* GLA: rows of the decay bottleneck */
+    float tau;                         /* GLA: decay temperature */
+    int32_t rot_dim, kv_rank;          /* latent attention: rotated channels per head / latent width */
+    int32_t kv_from;                   /* latent attention: layer whose cached latent is read, -1 = its own */
+    int32_t window;                    /* latent attention: position i sees j with 0 <= i - j < window; 0 = every earlier key */
+    int32_t rot_dims;                  /* leading channels of the rotated part that turn (pairs 2i, 2i+1) */
+    double rot_base;
+    float scale;                       /* multiplies the scores */
+    float yarn_factor;                 /* 0 = plain rotary; else YaRN with the next three */
+    float yarn_original, yarn_fast, yarn_slow;
+    int32_t ffn;                       /* fl_ffn_kind */
+    int32_t ff;                        /* dense: hidden width; MoE: hidden width of one expert */
+    float limit;
+    int32_t experts, top;              /* MoE */
+    int32_t shared_ff;                 /* MoE: hidden width of the shared expert, 0 = none */
+    float shared_limit;
+    int32_t reserved[4];
+} fl_layer_desc;
+
+typedef struct fl_stack_config {
+    int32_t arch;                      /* FL_ARCH_NIFUNEX */
+    int32_t vocab, width, n_layers;
+    float norm_eps;
+    int32_t compute_dtype;             /* FL_DTYPE_BF16: bf16 weights on the tensor-core path, bf16 cache; FL_DTYPE_F32: every product
+                                          and the cache in true 32-bit (weights are still stored as the bf16 values they were given) */
+    int32_t reserved[6];
+} fl_stack_config;
+
 /* ---- process / device -------------------------------------------------------------------------- */
 FL_EXPORT int fl_init(int device);                               /* cudaSetDevice + one-time setup; idempotent */
 FL_EXPORT const char* fl_last_error(void);                       /* thread-local, never NULL */
@@ -105,6 +155,9 @@ FL_EXPORT int fl_device_synchronize(void);
 
 /* ---- model (weights) --------------------------------------------------------------------------- */
 FL_EXPORT int fl_model_create(const fl_config* cfg, fl_model** out);
+/* A layered model: cfg->n_layers entries of `layers`.  Tensors then arrive by name through fl_model_put_tensor ("embed", "head",
+ * "final.norm", "l<i>.norm1|norm1b|norm2|norm2b", "l<i>.mix.*", "l<i>.mlp.*"); fl_model_finalize checks that all came. */
+FL_EXPORT int fl_model_create_layered(const fl_stack_config* cfg, const fl_layer_desc* layers, fl_model** out);
 /* Upload one tensor by its HuggingFace name (same names VarBuilder asks for).  f32/f16 inputs are rounded to
  * bf16 (round-to-nearest-even), as VarBuilder::from_tensors(.., DType::BF16, ..) does (main.rs:120).  The host
  * buffer may be freed on return.  q/k/v and gate/up are fused and row-permuted on upload. */
@@ -119,6 +172,11 @@ FL_EXPORT int fl_model_weight_bytes(fl_model* m, uint64_t* streamed_bytes); /* b
 
 /* ---- KV cache ---------------------------------------------------------------------------------- */
 FL_EXPORT int fl_cache_create(fl_model* m, int max_batch, int max_seq, fl_cache** out);
+/* A cache whose pages are handed out on demand: `max_slots` sequence slots (each with the recurrent state of the model's
+ * stateful layers) share a pool of ceil(pool_tokens / 64) pages; a slot takes pages as it grows, up to max_seq tokens, and
+ * fl_cache_slot_reset gives them back.  Layered models only (for them fl_cache_create is this with pool_tokens = max_batch x max_seq). */
+FL_EXPORT int fl_cache_create_pooled(fl_model* m, int max_slots, int max_seq, int pool_tokens, fl_cache** out);
+FL_EXPORT int fl_cache_pool_stats(fl_cache* c, int* pages_total, int* pages_free);
 FL_EXPORT int fl_cache_reset(fl_cache* c);                       /* kv length := 0 for every sequence */
 FL_EXPORT int fl_cache_kv_len(fl_cache* c, int* out);            /* tokens currently held (same for every sequence) */
 FL_EXPORT int fl_cache_fill_synthetic(fl_cache* c, int batch, int kv_len, uint64_t seed); /* benchmark: pretend a kv_len-token prefill */
@@ -145,6 +203,13 @@ FL_EXPORT int fl_decode_greedy_loop(fl_model* m, fl_cache* c, const uint32_t* fi
  * A cache is driven either by the uniform calls above or by slots; fl_cache_reset switches back. */
 FL_EXPORT int fl_forward_slots(fl_model* m, fl_cache* c, const int* slots, const uint32_t* ids, int n, int t, const size_t* rope_offsets,
                                float* logits_host);
+/* One step of a mixed batch (layered models): sequence i of the call lives in slot slots[i] and is fed counts[i] >= 1 new tokens
+ * (a portion of a prompt, or one decoded token) at the positions that follow what the slot already holds; ids holds the tokens of
+ * all sequences back to back.  want[k] indexes that flattened token list: logits_host receives f32 [n_want, vocab] in that order
+ * (n_want may be 0).  The result at a position does not depend on how its sequence was cut into calls or on what else is in the
+ * batch, beyond rounding. */
+FL_EXPORT int fl_forward_ragged(fl_model* m, fl_cache* c, const int* slots, const int* counts, int n, const uint32_t* ids,
+                                const int* want, int n_want, float* logits_host);
 FL_EXPORT int fl_cache_slot_reset(fl_cache* c, int slot);        /* the slot's sequence is finished: length := 0 */
 FL_EXPORT int fl_cache_slot_len(fl_cache* c, int slot, int* out);
 
