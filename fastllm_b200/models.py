@@ -766,15 +766,26 @@ class ContinuousBatcher:
     adapter's position rule -- Llama: the caller's position; Mistral / Qwen2: +1 per CALL (mistral.rs:234, qwen.rs:143).
     `cache` needs forward_slots(slots, ids, rope_offsets) -> [n, V], slot_reset(slot): a DeviceCache, or a stand-in in tests."""
 
-    def __init__(self, model, max_batch: int = 8, eos_token_id: int | None = 2, cache=None):
+    def __init__(self, model, max_batch: int = 8, eos_token_id: int | None = 2, cache=None, prefill_chunk: int | None = None):
+        """prefill_chunk (caches with forward_ragged, i.e. layered models): prompts are fed in portions of at most that many tokens
+        and every step is ONE mixed batch -- the next portion of each request still reading its prompt beside the single new token of
+        each request already decoding.  None: a prompt is prefilled alone in one call, then decoded in the shared steps."""
         self.model, self.max_batch, self.eos_token_id = model, max_batch, eos_token_id
+        self.prefill_chunk = prefill_chunk
         # the Mistral/Qwen2 adapters' offset rule (+1 per call); Llama and the layered decoder take true positions
         self.position_per_call = getattr(model, "position_per_call", getattr(model, "arch", "llama") != "llama")
-        self.cache = cache if cache is not None else DeviceCache(model.dev, max_batch, model._capacity())
+        if cache is not None:
+            self.cache = cache
+        elif hasattr(model, "new_device_cache"):
+            self.cache = model.new_device_cache(max_batch)
+        else:
+            self.cache = DeviceCache(model.dev, max_batch, model._capacity())
         self.steps = 0          # ragged decode forwards issued (tests / stats)
 
     def generate(self, prompts, max_tokens: int, temperature: float = 0.0):
         """-> one id list per prompt, in request order."""
+        if self.prefill_chunk and hasattr(self.cache, "forward_ragged"):
+            return self._generate_mixed(prompts, max_tokens, temperature)
         out = [[] for _ in prompts]
         waiting = list(range(len(prompts)))[::-1]
         free = list(range(self.max_batch))[::-1]
@@ -815,6 +826,55 @@ class ContinuousBatcher:
                 st = running[s]
                 st[1] += 1
                 take(logits[i].reshape(-1), st[0], s, st)
+        return out
+
+
+    def _generate_mixed(self, prompts, max_tokens: int, temperature: float):
+        """Mixed steps: a request takes a free slot as soon as there is one; each step carries, per running request, either the next
+        portion of its prompt (at most prefill_chunk tokens) or its one new token.  Sampling, EOS and the token budget are those of
+        generate(); a finished request gives its slot (pages and state) back."""
+        out = [[] for _ in prompts]
+        if max_tokens <= 0:
+            return out
+        waiting = list(range(len(prompts)))[::-1]
+        free = list(range(self.max_batch))[::-1]
+        running = {}            # slot -> [request, prompt tokens fed, LogitsProcessor, token to feed]
+        while waiting or running:
+            while waiting and free:
+                req, slot = waiting.pop(), free.pop()
+                running[slot] = [req, 0, LogitsProcessor(0, float(np.float32(temperature))), None]
+            slots = sorted(running)
+            toks, want = [], []
+            for s in slots:
+                req, fed, _, nxt = running[s]
+                prompt = prompts[req]
+                if fed < len(prompt):
+                    part = list(prompt[fed:fed + self.prefill_chunk])
+                    running[s][1] = fed + len(part)
+                    toks.append(part)
+                    want.append([len(part) - 1] if running[s][1] == len(prompt) else [])
+                else:
+                    toks.append([nxt])
+                    want.append([0])
+            logits = np.asarray(self.cache.forward_ragged(slots, toks, want))
+            self.steps += 1
+            row = 0
+            for s, w in zip(slots, want):
+                if not w:
+                    continue
+                st = running[s]
+                tok = st[2].sample(logits[row].reshape(-1))
+                row += 1
+                if self.eos_token_id is not None and tok == self.eos_token_id:
+                    done = True
+                else:
+                    out[st[0]].append(tok)
+                    st[3] = tok
+                    done = len(out[st[0]]) >= max_tokens
+                if done:
+                    running.pop(s)
+                    self.cache.slot_reset(s)
+                    free.append(s)
         return out
 
 
