@@ -273,6 +273,25 @@ void layered_finalize(LayeredModel& m) {
         std::lock_guard<std::mutex> g(g_routes_mu);
         g_routes.erase(&m);
     }
+    // serving precision: the projections whose shapes fit the tcgen05 GEMM's tiles (whole 64-column k blocks, 16-byte rows) run
+    // there; everything else, and every product of the exact mode, stays on the f32 FMA kernel
+    if (!m.f32 && !env_flag("FL_LAYERED_NO_TC")) {
+        auto fits = [](int N, int K) { return K % 64 == 0 && N % 8 == 0; };
+        auto map = [&](const uint16_t* p, int N, int K, CUtensorMap& tm, bool& ok) {
+            ok = p != nullptr && fits(N, K);
+            if (ok) tm = make_tmap_bf16(p, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128);
+        };
+        for (LayeredLayerW& lw : m.layers) {
+            const fl_layer_desc& d = lw.d;
+            map(lw.w_in, lw.n_in, m.W, lw.tm_in, lw.tc_in);
+            map(lw.w_o, m.W, d.heads * d.vdim, lw.tm_o, lw.tc_o);
+            if (d.ffn == FL_FFN_DENSE) { map(lw.w_gu, 2 * d.ff, m.W, lw.tm_gu, lw.tc_gu); map(lw.w_down, m.W, d.ff, lw.tm_down, lw.tc_down); }
+            if (d.ffn == FL_FFN_MOE && d.shared_ff > 0) {
+                map(lw.s_gu, 2 * d.shared_ff, m.W, lw.tm_sgu, lw.tc_sgu); map(lw.s_down, m.W, d.shared_ff, lw.tm_sdown, lw.tc_sdown);
+            }
+        }
+        map(m.head, m.V, m.W, m.tm_head, m.tc_head);
+    }
     m.finalized = true;
 }
 
@@ -364,12 +383,21 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
         y.sh_gu.alloc(R * 2 * std::max(m.max_ff, 1)); y.sh_act.alloc(R * std::max(m.max_ff, 1)); y.sh_o.alloc(R * W);
         y.route_w.alloc(P); y.route_sel.alloc(P); y.sgate.alloc(R);
         y.pair_row.alloc(P); y.pair_of.alloc(P); y.grp_off.alloc((size_t)m.max_experts + 2);
+        if (!m.f32) {
+            y.h_hi.alloc(R * W); y.h_lo.alloc(R * W);
+            y.u_hi.alloc(R * std::max(m.max_hv, 1)); y.u_lo.alloc(R * std::max(m.max_hv, 1));
+            y.act_hi.alloc(R * std::max(m.max_ff, 1)); y.act_lo.alloc(R * std::max(m.max_ff, 1));
+            // split-K slices of a tensor-core GEMM with <= 128 rows: ks * rows <= 256 (see pick_ksplit)
+            const size_t nmax = std::max<size_t>(std::max<size_t>(m.max_in, W), std::max<size_t>(2 * (size_t)m.max_ff, m.V));
+            if (y.gemm_out.n < 256 * nmax) y.gemm_out.alloc(256 * nmax);
+        }
         y.rows = R;
     }
     if (n_want > y.want_cap) {
         FL_CUDA(cudaStreamSynchronize(c.stream));
         const size_t N = std::max<size_t>(n_want, 2 * y.want_cap);
         y.hf.alloc(N * m.W); y.logits.alloc(N * m.V); y.h_logits.alloc(N * m.V);
+        if (!m.f32) { y.hf_hi.alloc(N * m.W); y.hf_lo.alloc(N * m.W); }
         y.want_cap = N;
     }
 }
@@ -379,6 +407,25 @@ static void gemm(LaunchCtx& lc, const char* tag, const float* A, int lda, const 
     LyGemm g{A, 0, lda, nullptr, Wt, 0, N, K, Y, 0, ldy, nullptr, R};
     launch(lc, tag, (uint64_t)N * K * 2, ly_gemm_kernel, dim3((N + kLyBN - 1) / kLyBN, (R + kLyBM - 1) / kLyBM, 1), dim3(256), 0, g);
 }
+// Y[R, N] = A[R, K] . Wt[N, K]^T on the tensor cores when the matrix has a descriptor (serving precision; A as hi | lo halves),
+// else on the exact kernel.  Split-K slices of the tensor-core GEMM are folded in slice order.
+static void gemm_tc_or_exact(fl_cache& c, LaunchCtx& lc, const char* tag, const float* A, const uint16_t* ahi, const uint16_t* alo, const uint16_t* Wt,
+                             const CUtensorMap& tm, bool tc, int N, int K, float* Y, int R) {
+    if (R <= 0) return;
+    if (!tc || ahi == nullptr) { gemm(lc, tag, A, K, Wt, N, K, Y, N, R); return; }
+    LayeredCache& y = *c.ly;
+    const int ks_plan = R <= 128 ? pick_ksplit((N + 127) / 128, (K + 63) / 64, R) : 1;
+    float* out = ks_plan == 1 ? Y : y.gemm_out.p;
+    FL_CHECK(ks_plan == 1 || (size_t)ks_plan * R * N <= y.gemm_out.n, FL_ERR_STATE, "internal: split-K scratch too small");
+    const int ks = dense_gemm(c, lc, tag, R, N, K, tm, out, ahi, alo);
+    FL_CHECK(ks == ks_plan, FL_ERR_STATE, "internal: split-K plan mismatch");
+    if (ks > 1) {
+        const size_t n = (size_t)R * N;
+        launch(lc, "sum_slices", 0, ly_sum_slices_kernel, dim3((unsigned)std::min<size_t>(4 * kNumSMs, (n + 255) / 256)), dim3(256), 0,
+               (const float*)out, ks, n, n, Y);
+    }
+}
+
 static void gemm_groups(LaunchCtx& lc, const char* tag, const LyGemm& g, int groups, int max_rows) {
     if (max_rows <= 0) return;
     launch(lc, tag, (uint64_t)groups * g.N * g.K * 2, ly_gemm_kernel, dim3((g.N + kLyBN - 1) / kLyBN, (max_rows + kLyBM - 1) / kLyBM, groups),
@@ -468,13 +515,15 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
     const int Ti = (int)T, W = m.W;
     const float eps = m.cfg.norm_eps;
     const int nthr = std::min(1024, std::max(64, (W + 31) / 32 * 32));
+    uint16_t *hhi = m.f32 ? nullptr : y.h_hi.p, *hlo = m.f32 ? nullptr : y.h_lo.p, *uhi = m.f32 ? nullptr : y.u_hi.p, *ulo = m.f32 ? nullptr : y.u_lo.p,
+             *ahi = m.f32 ? nullptr : y.act_hi.p, *alo = m.f32 ? nullptr : y.act_lo.p;
     launch(lc, "embed_norm", 0, ly_embed_norm_kernel, dim3(Ti), dim3(nthr), 0, (const uint16_t*)m.embed, st.tok, W, (const float*)m.layers[0].norm1, eps,
-           y.x.p, y.h.p);
+           y.x.p, y.h.p, hhi, hlo);
     for (int li = 0; li < m.L; ++li) {
         const LayeredLayerW& lw = m.layers[li];
         const fl_layer_desc& d = lw.d;
         const int H = d.heads, D = d.dim, Dv = d.vdim;
-        gemm(lc, "gemm_mix_in", y.h.p, W, lw.w_in, lw.n_in, W, y.proj.p, lw.n_in, Ti);
+        gemm_tc_or_exact(c, lc, "gemm_mix_in", y.h.p, hhi, hlo, lw.w_in, lw.tm_in, lw.tc_in, lw.n_in, W, y.proj.p, Ti);
         if (d.mixer == FL_MIXER_GLA) {
             launch(lc, "gla_decay", 0, ly_gla_decay_kernel, dim3(Ti), dim3(256), (size_t)d.decay_rank * 4, (const float*)y.proj.p, lw.n_in, lw.off_a,
                    d.decay_rank, (const float*)lw.a2, (const float*)lw.a2b, H * D, 1.f / d.tau, y.la.p);
@@ -482,7 +531,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
                        st.seq_pos0, H, D, Dv, (float)(1.0 / std::sqrt((double)D))};
             launch_gla_scan(lc, ga, n);
             launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)ga.o, (const float*)y.proj.p, lw.n_in, lw.off_g,
-                   (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p);
+                   (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
         } else {
             const int R = d.rot_dim, C = d.kv_rank;
             LatentAppendArgs aa{y.proj.p, lw.n_in, lw.off_q, lw.off_dkv, lw.dkv_norm, eps, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq,
@@ -498,18 +547,23 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
             // value expansion after the softmax: out[row, h, :] = W_uv[h] (sum_j p_j c_j)
             LyGemm ov{y.ol.p, C, H * C, nullptr, lw.uv, (long long)Dv * C, Dv, C, y.u.p, Dv, H * Dv, nullptr, Ti};
             gemm_groups(lc, "gemm_v_expand", ov, H, Ti);
+            if (lw.tc_o) {
+                const size_t nu = (size_t)Ti * H * Dv;
+                launch(lc, "split_hi_lo", 0, ly_split_kernel, dim3((unsigned)std::min<size_t>(4 * kNumSMs, (nu + 255) / 256)), dim3(256), 0,
+                       (const float*)y.u.p, nu, uhi, ulo);
+            }
         }
-        gemm(lc, "gemm_mix_out", y.u.p, H * Dv, lw.w_o, W, H * Dv, y.y.p, W, Ti);
+        gemm_tc_or_exact(c, lc, "gemm_mix_out", y.u.p, uhi, ulo, lw.w_o, lw.tm_o, lw.tc_o, W, H * Dv, y.y.p, Ti);
         const float* next1 = li + 1 < m.L ? m.layers[li + 1].norm1 : nullptr;
         launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm1b,
-               d.ffn != FL_FFN_NONE ? (const float*)lw.norm2 : next1, eps, W, y.h.p);
+               d.ffn != FL_FFN_NONE ? (const float*)lw.norm2 : next1, eps, W, y.h.p, hhi, hlo);
         if (d.ffn == FL_FFN_NONE) continue;
         const int F = d.ff;
         if (d.ffn == FL_FFN_DENSE) {
-            gemm(lc, "gemm_ff_in", y.h.p, W, lw.w_gu, 2 * F, W, y.gu.p, 2 * F, Ti);
+            gemm_tc_or_exact(c, lc, "gemm_ff_in", y.h.p, hhi, hlo, lw.w_gu, lw.tm_gu, lw.tc_gu, 2 * F, W, y.gu.p, Ti);
             launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                   (const int*)nullptr, Ti, y.act.p);
-            gemm(lc, "gemm_ff_out", y.act.p, F, lw.w_down, W, F, y.y.p, W, Ti);
+                   (const int*)nullptr, Ti, y.act.p, lw.tc_down ? ahi : (uint16_t*)nullptr, alo);
+            gemm_tc_or_exact(c, lc, "gemm_ff_out", y.act.p, ahi, alo, lw.w_down, lw.tm_down, lw.tc_down, W, F, y.y.p, Ti);
         } else {
             const int E = d.experts, top = d.top, P = Ti * top;
             launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, (const float*)y.h.p, W, (const float*)lw.router, E, top,
@@ -519,26 +573,28 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
             LyGemm g1{y.h.p, 0, W, y.pair_row.p, lw.w_gu, (long long)2 * F * W, 2 * F, W, y.gu.p, 0, 2 * F, y.grp_off.p, P};
             gemm_groups(lc, "gemm_moe_in", g1, E, P);
             launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (P * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                   (const int*)nullptr, P, y.act.p);
+                   (const int*)nullptr, P, y.act.p, (uint16_t*)nullptr, (uint16_t*)nullptr);
             LyGemm g2{y.act.p, 0, F, nullptr, lw.w_down, (long long)W * F, W, F, y.eo.p, 0, W, y.grp_off.p, P};
             gemm_groups(lc, "gemm_moe_out", g2, E, P);
             const float* sh = nullptr;
             if (d.shared_ff > 0) {
                 const int Fs = d.shared_ff;
-                gemm(lc, "gemm_shared_in", y.h.p, W, lw.s_gu, 2 * Fs, W, y.sh_gu.p, 2 * Fs, Ti);
+                gemm_tc_or_exact(c, lc, "gemm_shared_in", y.h.p, hhi, hlo, lw.s_gu, lw.tm_sgu, lw.tc_sgu, 2 * Fs, W, y.sh_gu.p, Ti);
                 launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * Fs + 255) / 256)), dim3(256), 0, (const float*)y.sh_gu.p, Fs,
-                       d.shared_limit, (const int*)nullptr, Ti, y.sh_act.p);
-                gemm(lc, "gemm_shared_out", y.sh_act.p, Fs, lw.s_down, W, Fs, y.sh_o.p, W, Ti);
+                       d.shared_limit, (const int*)nullptr, Ti, y.sh_act.p, lw.tc_sdown ? ahi : (uint16_t*)nullptr, alo);
+                gemm_tc_or_exact(c, lc, "gemm_shared_out", y.sh_act.p, ahi, alo, lw.s_down, lw.tm_sdown, lw.tc_sdown, W, Fs, y.sh_o.p, Ti);
                 sh = y.sh_o.p;
             }
             launch(lc, "moe_combine", 0, ly_moe_combine_kernel, dim3((W + 255) / 256, Ti), dim3(256), 0, (const float*)y.eo.p, (const int*)y.pair_of.p,
                    (const float*)y.route_w.p, top, sh, (const float*)y.sgate.p, W, y.y.p);
         }
-        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm2b, next1, eps, W, y.h.p);
+        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm2b, next1, eps, W, y.h.p,
+               hhi, hlo);
     }
     if (n_want > 0) {
-        launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, y.hf.p);
-        gemm(lc, "gemm_head", y.hf.p, W, m.head, m.V, W, y.logits.p, m.V, n_want);
+        launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, y.hf.p,
+               m.tc_head ? y.hf_hi.p : (uint16_t*)nullptr, y.hf_lo.p);
+        gemm_tc_or_exact(c, lc, "gemm_head", y.hf.p, m.tc_head ? y.hf_hi.p : nullptr, y.hf_lo.p, m.head, m.tm_head, m.tc_head, m.V, W, y.logits.p, n_want);
         FL_CUDA(cudaMemcpyAsync(y.h_logits.p, y.logits.p, (size_t)n_want * m.V * 4, cudaMemcpyDeviceToHost, c.stream));
     }
     for (int i = 0; i < n; ++i) c.slot_len[slots[i]] += counts[i];

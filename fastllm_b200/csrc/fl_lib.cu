@@ -1000,7 +1000,6 @@ static void enqueue_forward(fl_cache& c, LaunchCtx& lc, int b, int t, bool loop_
 // ------------------------------------------------------------------------------------------------------------------
 constexpr int kDenseMaxSplit = 16;    // upper bound on the split-K slices of a decode GEMM (see pick_ksplit)
 
-static int pick_ksplit(int tiles, int nk, int R);
 // rows per expert block of the grouped expert GEMMs = their N tile: the smallest of 16 / 32 / 64 / 128 that holds every row
 static int moe_group_cap(int Rm) { return Rm <= 16 ? 16 : (Rm <= 32 ? 32 : (Rm <= 64 ? 64 : 128)); }
 
@@ -1095,7 +1094,7 @@ static void launch_gemm_tc(cudaStream_t st, bool pdl, int items, const CUtensorM
 // Split-K factor of a swap-AB (decode) GEMM: the one whose work items (output tiles x k slices) fill whole waves of the 148
 // persistent CTAs best, counting the padding of the last k slice; fewer, longer items win ties (pipeline fill / epilogue per item).
 // The consumer sums the slices in a fixed order, so a row's bytes read grow with ks: capped by the row count.
-static int pick_ksplit(int tiles, int nk, int R) {
+int pick_ksplit(int tiles, int nk, int R) {
     const int maxks = std::max(1, std::min(std::min(kDenseMaxSplit, std::max(2, 256 / std::max(R, 1))), nk / 4));
     int best = 1;
     double best_eff = 0.0;
@@ -1114,8 +1113,8 @@ static int pick_ksplit(int tiles, int nk, int R) {
 //   R <= 128 (decode batches, short prefills): swap-AB -- the weights are the 128-row MMA operand, the activations a tiny
 //             N = R tile, the result is stored transposed; the only large shared-memory traffic is the weight stream.
 //   R  > 128 (prefill): tokens are the M dimension, 128 x 128 output tiles.
-static int dense_gemm(fl_cache& c, LaunchCtx& lc, const char* tag, int R, int N, int K, const CUtensorMap& tmW, float* out,
-                      const uint16_t* xhi = nullptr, const uint16_t* xlo = nullptr, uint16_t* silu_hi = nullptr, uint16_t* silu_lo = nullptr) {
+int dense_gemm(fl_cache& c, LaunchCtx& lc, const char* tag, int R, int N, int K, const CUtensorMap& tmW, float* out,
+               const uint16_t* xhi, const uint16_t* xlo, uint16_t* silu_hi, uint16_t* silu_lo) {
     if (!xhi) { xhi = c.dw.xhi.p; xlo = c.dw.xlo.p; }
     const int nk = (K + kGemmBK - 1) / kGemmBK;
     const bool swap = R <= 128;
@@ -1172,8 +1171,8 @@ static int dense_gemm(fl_cache& c, LaunchCtx& lc, const char* tag, int R, int N,
 // Grouped swap-AB GEMM over this rank's experts (decode batches): group j multiplies ITS gathered rows (block j of xhi / xlo,
 // `cap` rows, cnt[j] valid) with ITS matrix (block j of the stacked weights, Ne rows): out[ks][j * cap + n][Ne].  ONE launch over
 // (expert, weight tile, k slice) work items; an expert without rows costs nothing.  Returns the split-K factor.
-static int dense_gemm_grouped(fl_cache& c, LaunchCtx& lc, const char* tag, int groups, int cap, int Ne, int K, const CUtensorMap& tmWall,
-                              float* out, const uint16_t* xhi, const uint16_t* xlo, const int* cnt) {
+int dense_gemm_grouped(fl_cache& c, LaunchCtx& lc, const char* tag, int groups, int cap, int Ne, int K, const CUtensorMap& tmWall,
+                       float* out, const uint16_t* xhi, const uint16_t* xlo, const int* cnt) {
     const int nk = (K + kGemmBK - 1) / kGemmBK;
     const int tiles = groups * ((Ne + kGemmBM - 1) / kGemmBM);
     const int ks = pick_ksplit(tiles, nk, cap);

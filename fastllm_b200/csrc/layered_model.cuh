@@ -39,6 +39,9 @@ struct LayeredLayerW {
     uint16_t *w_gu = nullptr, *w_down = nullptr;        // [groups][2 ff, W] (gate rows then up rows), [groups][W, ff]
     uint16_t *s_gu = nullptr, *s_down = nullptr;        // shared expert
     float *router = nullptr, *shared_gate = nullptr;    // [experts, W], [W] f32
+    // serving precision: TMA descriptors of the matrices whose shapes admit the tensor-core GEMM (tc_* says which)
+    CUtensorMap tm_in{}, tm_o{}, tm_gu{}, tm_down{}, tm_sgu{}, tm_sdown{};
+    bool tc_in = false, tc_o = false, tc_gu = false, tc_down = false, tc_sgu = false, tc_sdown = false;
 };
 
 struct RopeSpec {                       // one distinct rotary configuration (tables are built per cache: they depend on max_seq)
@@ -61,6 +64,8 @@ struct LayeredModel {
     DevBuf<uint8_t> slab;
     uint16_t *embed = nullptr, *head = nullptr;
     float* final_norm = nullptr;
+    CUtensorMap tm_head{};
+    bool tc_head = false;
     std::set<std::string> have;
     std::vector<std::string> expected;
     int ignored = 0;
@@ -88,8 +93,8 @@ struct LayeredCache {
     DevBuf<float> x, h, y, proj, la, u, go, qa, ol, gu, act, eo, sh_gu, sh_act, sh_o, route_w, sgate, hf, logits;
     DevBuf<int> route_sel, pair_row, pair_of, grp_off;
     PinnedBuf<float> h_logits;
-    // bf16 tensor-core path: hi/lo split of a GEMM's activations
-    DevBuf<uint16_t> xhi, xlo;
+    // serving precision: hi/lo halves of the activations that feed tensor-core GEMMs, and the split-K slices of their outputs
+    DevBuf<uint16_t> h_hi, h_lo, u_hi, u_lo, act_hi, act_lo, hf_hi, hf_lo;
     DevBuf<float> gemm_out;
 };
 

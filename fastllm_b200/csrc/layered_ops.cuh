@@ -45,10 +45,30 @@ __device__ __forceinline__ float block_sum(float v, float* red) {      // red: >
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.f / (1.f + expf(-z)); }
 
+// The tensor-core GEMMs take an f32 activation as two bf16 halves, v = hi + lo (about 16 mantissa bits): written by the kernel
+// that produces the activation, beside the f32 copy.  hi == nullptr: the exact path, nothing to write.
+__device__ __forceinline__ void split_store(uint16_t* hi, uint16_t* lo, size_t i, float v) {
+    if (hi == nullptr) return;
+    const uint16_t h = f32_to_bf16_rne(v);
+    hi[i] = h;
+    lo[i] = f32_to_bf16_rne(v - __uint_as_float((uint32_t)h << 16));
+}
+static __global__ void ly_split_kernel(const float* __restrict__ x, size_t n, uint16_t* __restrict__ hi, uint16_t* __restrict__ lo) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) split_store(hi, lo, i, x[i]);
+}
+// out[i] = sum over the split-K slices of a tensor-core GEMM, in slice order
+static __global__ void ly_sum_slices_kernel(const float* __restrict__ y, int nsl, size_t stride, size_t n, float* __restrict__ out) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        float t = 0.f;
+        for (int k = 0; k < nsl; ++k) t += y[(size_t)k * stride + i];
+        out[i] = t;
+    }
+}
+
 // ---- embedding + first norm ------------------------------------------------------------------------------------------------
 // x[row] = embed[tok[row]];  h[row] = x / sqrt(mean x^2 + eps) * (1 + w)
 static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, const int* __restrict__ tok, int W, const float* __restrict__ nw,
-                                            float eps, float* __restrict__ x, float* __restrict__ h) {
+                                            float eps, float* __restrict__ x, float* __restrict__ h, uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const int row = blockIdx.x;
     const uint16_t* e = embed + (size_t)tok[row] * W;
@@ -61,12 +81,17 @@ static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, 
     }
     const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
     float* hr = h + (size_t)row * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = xr[c] * r * (1.f + nw[c]);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = xr[c] * r * (1.f + nw[c]);
+        hr[c] = v;
+        split_store(hhi, hlo, (size_t)row * W + c, v);
+    }
 }
 
 // x[row] += norm(y[row]; wb);  then, if wnext, h[row] = norm(x[row]; wnext)      (norm: weight stored around zero)
 static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
-                                           const float* __restrict__ wnext, float eps, int W, float* __restrict__ h) {
+                                           const float* __restrict__ wnext, float eps, int W, float* __restrict__ h, uint16_t* __restrict__ hhi,
+                                           uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const int row = blockIdx.x;
     const float* yr = y + (size_t)row * W;
@@ -83,19 +108,27 @@ static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* _
     if (wnext == nullptr) return;
     const float r2 = 1.f / sqrtf(block_sum(s2, red) / (float)W + eps);
     float* hr = h + (size_t)row * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = xr[c] * r2 * (1.f + wnext[c]);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = xr[c] * r2 * (1.f + wnext[c]);
+        hr[c] = v;
+        split_store(hhi, hlo, (size_t)row * W + c, v);
+    }
 }
 
 // hf[i] = norm(x[want[i]]; w): the rows that go on to the vocabulary projection
 static __global__ void ly_final_norm_kernel(const float* __restrict__ x, const int* __restrict__ want, const float* __restrict__ w, float eps, int W,
-                                            float* __restrict__ hf) {
+                                            float* __restrict__ hf, uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const float* xr = x + (size_t)want[blockIdx.x] * W;
     float ss = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) ss += xr[c] * xr[c];
     const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
     float* hr = hf + (size_t)blockIdx.x * W;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) hr[c] = xr[c] * r * (1.f + w[c]);
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = xr[c] * r * (1.f + w[c]);
+        hr[c] = v;
+        split_store(hhi, hlo, (size_t)blockIdx.x * W + c, v);
+    }
 }
 
 // ---- exact GEMM: Y[p, n] = sum_k A[row(p), k] * W[n, k]   (A f32, W bf16 bit patterns, f32 FMA in ascending k) ----------------------
@@ -256,7 +289,7 @@ static __global__ void __launch_bounds__(kGlaVS * kGlaDG) ly_gla_scan_kernel(Gla
 
 // u[row, h, :] = o[row, h, :] / sqrt(mean o^2 + eps) * w[:] * silu(g[row, h, :])     (one warp per (row, head))
 static __global__ void ly_gla_out_kernel(const float* __restrict__ o, const float* __restrict__ proj, int ldp, int off_g, const float* __restrict__ w,
-                                         float eps, int T, int H, int Dv, float* __restrict__ u) {
+                                         float eps, int T, int H, int Dv, float* __restrict__ u, uint16_t* __restrict__ uhi, uint16_t* __restrict__ ulo) {
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (item >= T * H) return;
     const int row = item / H, hd = item % H;
@@ -268,7 +301,9 @@ static __global__ void ly_gla_out_kernel(const float* __restrict__ o, const floa
     float* up = u + (size_t)row * H * Dv + hd * Dv;
     for (int c = lane; c < Dv; c += 32) {
         const float g = gp[c];
-        up[c] = op[c] * r * w[c] * (g * sigmoidf_(g));
+        const float v = op[c] * r * w[c] * (g * sigmoidf_(g));
+        up[c] = v;
+        split_store(uhi, ulo, (size_t)row * H * Dv + hd * Dv + c, v);
     }
 }
 
@@ -388,14 +423,17 @@ static __global__ void __launch_bounds__(kLatWarps * 32) ly_latent_attn_kernel(L
 
 // ---- feed-forward ----------------------------------------------------------------------------------------------------------
 // act[p, f] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[p, f], limit),  u = clamp(gu[p, F + f], -limit, limit);  p < *count
-static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float limit, const int* __restrict__ count, int rows, float* __restrict__ act) {
+static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float limit, const int* __restrict__ count, int rows, float* __restrict__ act,
+                                     uint16_t* __restrict__ ahi, uint16_t* __restrict__ alo) {
     const int n = count ? *count : rows;
     const size_t total = (size_t)n * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t p = i / F, f = i - p * F;
         const float g = fminf(gu[p * 2 * F + f], limit);
         const float u = fminf(fmaxf(gu[p * 2 * F + F + f], -limit), limit);
-        act[i] = g * sigmoidf_(1.702f * g) * (u + 1.f);
+        const float v = g * sigmoidf_(1.702f * g) * (u + 1.f);
+        act[i] = v;
+        split_store(ahi, alo, i, v);
     }
 }
 

@@ -163,3 +163,14 @@ struct fl_cache {
     fl::DevBuf<float> tp_local;      // [max_batch, V] this rank's logits slice
     bool poisoned = false;
 };
+
+namespace fl {
+// The dense tensor-core GEMM of fl_lib.cu (tcgen05 / TMEM / TMA, hi|lo activation halves), shared with the layered decoder:
+// out[ks][R, N] (f32, row stride N, slice stride R * N) = (xhi + xlo)[R, K] . W[N, K]^T; returns the number of split-K slices
+// (R <= 128: pick_ksplit of the weight tiles; R > 128: always 1), which the consumer sums in a fixed order.
+int pick_ksplit(int tiles, int nk, int R);
+int dense_gemm(fl_cache& c, LaunchCtx& lc, const char* tag, int R, int N, int K, const CUtensorMap& tmW, float* out,
+               const uint16_t* xhi = nullptr, const uint16_t* xlo = nullptr, uint16_t* silu_hi = nullptr, uint16_t* silu_lo = nullptr);
+int dense_gemm_grouped(fl_cache& c, LaunchCtx& lc, const char* tag, int groups, int cap, int Ne, int K, const CUtensorMap& tmWall,
+                       float* out, const uint16_t* xhi, const uint16_t* xlo, const int* cnt);
+}  // namespace fl
