@@ -50,6 +50,8 @@ WORKLOADS = {
     "minilm_256x128": ("minilm", 256, 128, "all-MiniLM-L6-v2 (BertModel) embeddings, batch 256 x seq 128"),
     "mixtral8x7b_b32": ("mixtral8x7b", 32, 2048, "Mixtral-8x7B bf16 top-2 MoE decode, batch 32, 2k context"),
     "qwen25_7b_prefill4k": ("qwen25_7b", 1, 4096, "Qwen2.5-7B bf16 prefill 4096 tokens (+ 256 decode steps reported beside it)"),
+    "nifunex_vs_mixtral": ("nifunex", 8, 2048, "layered decoder (Nifunex: GLA + windowed latent attention + MoE with shared expert) beside Mixtral "
+                           "at equal width / experts / layers: 2048-token prefill and batch-8 decode at 2k context, random weights"),
 }
 QWEN_PREFILL_TFLOP_4K = 56.83         # 53.46 linear + 3.37 causal attention
 MINILM_FLOP_PER_TOKEN = 22.41e6      # 2 x 10.617 M linear + 4 T H 6 attention at T = 128
@@ -343,7 +345,7 @@ def run_reference(args, rank):
     if rank != 0:
         return
     arch, batch, ctx, desc = WORKLOADS[args.workload]
-    if args.workload in ("mixtral8x7b_b32", "qwen25_7b_prefill4k"):
+    if args.workload in ("mixtral8x7b_b32", "qwen25_7b_prefill4k", "nifunex_vs_mixtral"):
         print(json.dumps({"impl": "reference", "unavailable": f"no CPU leg for workload {args.workload}: the reference does not wire Mixtral "
                           "and a 4096-token f32 prefill of a 7B model does not fit a bounded CPU sample; the decode workloads carry the CPU baseline"}),
               flush=True)
@@ -842,6 +844,124 @@ def run_prefill(args, rank, world, local_rank):
     barrier()
 
 
+def _nifunex_config(width, ff, layers, vocab, window):
+    """A layered-decoder config at Mixtral-like sizes: heads of 128 channels, 8 experts top-2 plus a shared expert, every other
+    layer recurrent (GLA), every second attention layer reading the cache of the one before it."""
+    H = width // 128
+    ly = []
+    for i in range(layers):
+        mlp = {"kind": "moe", "expert": {"ff": ff, "limit": 7.0}, "router": {"experts": 8, "top": 2}, "shared": {"ff": ff, "limit": 7.0}}
+        if i % 2 == 0:
+            ly.append({"type": "gla", "mixer": {"heads": H, "dim": 128, "vdim": 128, "tau": 16.0}, "mlp": mlp})
+        else:
+            m = {"heads": H, "dim": 96, "rot_dim": 32, "vdim": 128, "kv_rank": 512, "scale": 128 ** -0.5, "mask": {"size": window},
+                 "rot": {"base": 10000.0, "dims": 32}}
+            if i % 4 == 3:
+                m["kv_from"] = i - 2
+            ly.append({"type": "latent_attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Nifunex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": ly}
+
+
+def _profile_table(prof):
+    agg = {}
+    for p in prof:
+        a = agg.setdefault(p["kernel"], {"launches": 0, "ms": 0.0, "bytes": 0})
+        a["launches"] += p["launches"]; a["ms"] += p["ms"]; a["bytes"] += p["bytes"]
+    hbm, _ = peaks("hbm")
+    out = []
+    for k, a in sorted(agg.items(), key=lambda kv: -kv[1]["ms"]):
+        r = {"kernel": k, "launches": a["launches"], "ms": round(a["ms"], 4)}
+        if a["bytes"] and a["ms"] > 0:
+            r["weight_GBs"] = round(a["bytes"] / (a["ms"] / 1e3) / 1e9, 1)
+            r["frac_of_hbm"] = round(a["bytes"] / (a["ms"] / 1e3) / 1e9 / hbm, 3)
+        out.append(r)
+    return out
+
+
+def run_layered_compare(args, local_rank):
+    """--workload nifunex_vs_mixtral (one GPU): the layered decoder and Mixtral at the same width / experts / layer count, random
+    weights -- one 2048-token prefill and batch-8 decode steps at a 2k context, through the public calls (host ids in, logits
+    out), with the per-kernel CUDA-event profile of one call of each kind."""
+    import torch
+    from fastllm_b200 import models
+    batch, T, steps, warm = 8, 2048, max(4, min(args.steps, 32)), 3
+    sizes = [("w1024", 1024, 2816, 4), ("w2048", 2048, 5632, 4), ("w4096", 4096, 14336, 4)]
+    vocab, window = 32000, 1024
+    results = {}
+
+    def timed(fn, n):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / n
+
+    with ClockSampler(local_rank) as clk:
+        t_wall0 = time.time()
+        for name, width, ff, layers in sizes:
+            rec = {"width": width, "expert_ff": ff, "layers": layers, "experts": 8, "top": 2, "window": window}
+            # ---- the layered decoder ----
+            cfg = _nifunex_config(width, ff, layers, vocab, window)
+            model, _ = models.NifunexWithConfig.initialize_model(cfg, None, "bf16", local_rank, random_seed=0, std=0.02, decay_rank=64)
+            cache = model.new_device_cache(max_batch=batch, max_seq=T + 64, pool_tokens=batch * (T + 64))
+            ids = (np.arange(T, dtype=np.uint64) * 7919 % (vocab - 5) + 3).astype(np.uint32)
+
+            def prefill():
+                cache.slot_reset(0)
+                cache.forward_ragged([0], [ids], None)
+            dt_p = timed(prefill, max(2, steps // 4))
+            models.prof_begin(); prefill(); prof_p = models.prof_end()
+            for s in range(1, batch):
+                cache.forward_ragged([s], [ids], None)
+            slots = list(range(batch))
+
+            def decode():
+                cache.forward_ragged(slots, [[7 + s] for s in slots], None)
+            dt_d = timed(decode, steps)
+            models.prof_begin(); decode(); prof_d = models.prof_end()
+            rec["nifunex"] = {"prefill_tok_s": T / dt_p, "prefill_ms": dt_p * 1e3, "decode_tok_s": batch / dt_d, "decode_ms_per_step": dt_d * 1e3,
+                              "weight_bytes": model.dev.streamed_bytes(), "prefill_kernels": _profile_table(prof_p), "decode_kernels": _profile_table(prof_d)}
+            del cache, model
+            # ---- Mixtral at the same sizes ----
+            cf = models.ConfigFile(width, ff, vocab, layers, width // 128, max(1, width // 512), 1e-5, 1e6, 32768, window, num_local_experts=8, num_experts_per_tok=2)
+            mx, _ = models.MixtralWithConfig.initialize_model(cf, None, "bf16", local_rank, random_seed=0, std=0.02)
+            mc = models.DeviceCache(mx.dev, batch, T + 64)
+            ids2 = ids[None]
+
+            def prefill_m():
+                mc.reset()
+                mc.forward_slots([0], ids2, [0])
+            dt_pm = timed(prefill_m, max(2, steps // 4))
+            models.prof_begin(); prefill_m(); prof_pm = models.prof_end()
+            for s in range(1, batch):
+                mc.forward_slots([s], ids2, [0])
+            pos = [T] * batch
+
+            def decode_m():
+                mc.forward_slots(slots, np.asarray([[7 + s] for s in slots], dtype=np.uint32), pos)
+                for i in range(batch):
+                    pos[i] += 1
+            dt_dm = timed(decode_m, steps)
+            models.prof_begin(); decode_m(); prof_dm = models.prof_end()
+            rec["mixtral"] = {"prefill_tok_s": T / dt_pm, "prefill_ms": dt_pm * 1e3, "decode_tok_s": batch / dt_dm, "decode_ms_per_step": dt_dm * 1e3,
+                              "weight_bytes": mx.dev.streamed_bytes(), "prefill_kernels": _profile_table(prof_pm), "decode_kernels": _profile_table(prof_dm)}
+            del mc, mx
+            results[name] = rec
+        t_wall1 = time.time()
+        time.sleep(0.12)
+    big = results[sizes[-1][0]]
+    print(json.dumps({"metric": "decode_tokens_per_s", "value": big["nifunex"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+                      "ms_per_step": big["nifunex"]["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                      "data": "synthetic",
+                      "config": {"workload": WORKLOADS[args.workload][3], "batch": batch, "context": T, "timing": "wall clock around the public call "
+                                 "(host ids in, f32 logits out) with a device synchronise on both sides; per-kernel figures are CUDA events",
+                                 "l2": "weights of a step exceed L2 at every size"},
+                      "clocks": clk.summary(t_wall0, t_wall1), "sizes": results}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -872,7 +992,10 @@ def main():
     import __graft_entry__ as g
     if rank == 0 or not os.path.exists(os.path.join(ROOT, "fastllm_b200", "libfastllm_b200.so")):
         g.build()
-    if args.workload == "minilm_256x128":
+    if args.workload == "nifunex_vs_mixtral":
+        if rank == 0:
+            run_layered_compare(args, local_rank)
+    elif args.workload == "minilm_256x128":
         run_minilm(args, rank, world, local_rank)
     elif args.workload == "qwen25_7b_prefill4k":
         run_prefill(args, rank, world, local_rank)

@@ -98,7 +98,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             lw.off_q = 0; lw.off_k = (int)(H * D); lw.off_v = (int)(2 * H * D); lw.off_g = lw.off_v + (int)(H * Dv);
             lw.off_a = lw.off_g + (int)(H * Dv);
             lw.n_in = lw.off_a + d.decay_rank;
-            reg(&lw.a2, H * D * d.decay_rank * 4); reg(&lw.a2b, H * D * 4); reg(&lw.hnorm, Dv * 4);
+            reg(&lw.a2, H * D * d.decay_rank * 2); reg(&lw.a2b, H * D * 4); reg(&lw.hnorm, Dv * 4);
             lw.gla_index = (int)m.gla_layers.size();
             m.gla_layers.push_back(i);
             m.max_hd = std::max<int>(m.max_hd, (int)(H * D));
@@ -170,7 +170,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             mat(p + "mix.q", lw.w_in, lw.off_q, H * D, W); mat(p + "mix.k", lw.w_in, lw.off_k, H * D, W);
             mat(p + "mix.v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "mix.g", lw.w_in, lw.off_g, H * Dv, W);
             mat(p + "mix.a1", lw.w_in, lw.off_a, d.decay_rank, W);
-            vec(p + "mix.a2", lw.a2, H * D, d.decay_rank); vec(p + "mix.a2.b", lw.a2b, H * D, 1); vec(p + "mix.norm", lw.hnorm, Dv, 1);
+            mat(p + "mix.a2", lw.a2, 0, H * D, d.decay_rank); vec(p + "mix.a2.b", lw.a2b, H * D, 1); vec(p + "mix.norm", lw.hnorm, Dv, 1);
         } else {
             const int64_t Rr = d.rot_dim, C = d.kv_rank;
             mat(p + "mix.q", lw.w_in, 0, H * (D + Rr), W);
@@ -289,6 +289,15 @@ void layered_finalize(LayeredModel& m) {
             if (d.ffn == FL_FFN_MOE && d.shared_ff > 0) {
                 map(lw.s_gu, 2 * d.shared_ff, m.W, lw.tm_sgu, lw.tc_sgu); map(lw.s_down, m.W, d.shared_ff, lw.tm_sdown, lw.tc_sdown);
             }
+            if (d.ffn == FL_FFN_MOE && fits(2 * d.ff, m.W) && fits(m.W, d.ff)) {
+                lw.tc_moe = true;
+                lw.tm_gu = make_tmap_bf16(lw.w_gu, (uint64_t)d.experts * 2 * d.ff, (uint64_t)m.W, (uint64_t)m.W, 128);
+                lw.tm_down = make_tmap_bf16(lw.w_down, (uint64_t)d.experts * m.W, (uint64_t)d.ff, (uint64_t)d.ff, 128);
+                for (int e = 0; e < d.experts; ++e) {
+                    lw.tm_egu.push_back(make_tmap_bf16(lw.w_gu + (size_t)e * 2 * d.ff * m.W, 2 * (uint64_t)d.ff, (uint64_t)m.W, (uint64_t)m.W, 128));
+                    lw.tm_edown.push_back(make_tmap_bf16(lw.w_down + (size_t)e * m.W * d.ff, (uint64_t)m.W, (uint64_t)d.ff, (uint64_t)d.ff, 128));
+                }
+            }
         }
         map(m.head, m.V, m.W, m.tm_head, m.tc_head);
     }
@@ -389,7 +398,23 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
             y.act_hi.alloc(R * std::max(m.max_ff, 1)); y.act_lo.alloc(R * std::max(m.max_ff, 1));
             // split-K slices of a tensor-core GEMM with <= 128 rows: ks * rows <= 256 (see pick_ksplit)
             const size_t nmax = std::max<size_t>(std::max<size_t>(m.max_in, W), std::max<size_t>(2 * (size_t)m.max_ff, m.V));
-            if (y.gemm_out.n < 256 * nmax) y.gemm_out.alloc(256 * nmax);
+            size_t need = 256 * nmax;
+            size_t gx_rows = 0;
+            for (const LayeredLayerW& lw : m.layers) {          // grouped expert GEMMs: [slices][experts * cap rows][2 ff | W]
+                if (!lw.tc_moe) continue;
+                const int E = lw.d.experts, F = lw.d.ff;
+                gx_rows = std::max<size_t>(gx_rows, (size_t)E * 128);
+                for (int cap = 16; cap <= 128; cap *= 2) {
+                    const int k1 = pick_ksplit(E * ((2 * F + 127) / 128), (int)(W + 63) / 64, cap), k2 = pick_ksplit(E * ((int)(W + 127) / 128), (F + 63) / 64, cap);
+                    need = std::max(need, std::max((size_t)k1 * E * cap * 2 * F, (size_t)k2 * E * cap * W));
+                }
+            }
+            if (y.gemm_out.n < need) y.gemm_out.alloc(need);
+            if (gx_rows > 0 && y.gx_hi.n == 0) {
+                y.gx_hi.alloc(gx_rows * W, true); y.gx_lo.alloc(gx_rows * W, true);
+                y.ga_hi.alloc(gx_rows * std::max(m.max_ff, 1), true); y.ga_lo.alloc(gx_rows * std::max(m.max_ff, 1), true);
+                y.grp_cnt.alloc((size_t)m.max_experts + 1, true);
+            }
         }
         y.rows = R;
     }
@@ -525,10 +550,10 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
         const int H = d.heads, D = d.dim, Dv = d.vdim;
         gemm_tc_or_exact(c, lc, "gemm_mix_in", y.h.p, hhi, hlo, lw.w_in, lw.tm_in, lw.tc_in, lw.n_in, W, y.proj.p, Ti);
         if (d.mixer == FL_MIXER_GLA) {
-            launch(lc, "gla_decay", 0, ly_gla_decay_kernel, dim3(Ti), dim3(256), (size_t)d.decay_rank * 4, (const float*)y.proj.p, lw.n_in, lw.off_a,
-                   d.decay_rank, (const float*)lw.a2, (const float*)lw.a2b, H * D, 1.f / d.tau, y.la.p);
-            GlaArgs ga{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, y.la.p, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0, st.seq_slot,
-                       st.seq_pos0, H, D, Dv, (float)(1.0 / std::sqrt((double)D))};
+            // decay pre-activation through the rank-r bottleneck: z = W_a2 a (the bias and the sigmoid^(1/tau) are applied by the scan)
+            gemm(lc, "gemm_gla_decay", y.proj.p + lw.off_a, lw.n_in, lw.a2, H * D, d.decay_rank, y.la.p, H * D, Ti);
+            GlaArgs ga{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, y.la.p, lw.a2b, 1.f / d.tau, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0,
+                       st.seq_slot, st.seq_pos0, H, D, Dv, (float)(1.0 / std::sqrt((double)D))};
             launch_gla_scan(lc, ga, n);
             launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)ga.o, (const float*)y.proj.p, lw.n_in, lw.off_g,
                    (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
@@ -568,16 +593,8 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
             const int E = d.experts, top = d.top, P = Ti * top;
             launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, (const float*)y.h.p, W, (const float*)lw.router, E, top,
                    (const float*)lw.shared_gate, y.route_sel.p, y.route_w.p, y.sgate.p);
-            launch(lc, "moe_lists", 0, ly_moe_lists_kernel, dim3(1), dim3(std::min(1024, (E + 31) / 32 * 32)), (size_t)(E + 1) * 4,
-                   (const int*)y.route_sel.p, Ti, top, E, y.grp_off.p, y.pair_row.p, y.pair_of.p);
-            LyGemm g1{y.h.p, 0, W, y.pair_row.p, lw.w_gu, (long long)2 * F * W, 2 * F, W, y.gu.p, 0, 2 * F, y.grp_off.p, P};
-            gemm_groups(lc, "gemm_moe_in", g1, E, P);
-            launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (P * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                   (const int*)nullptr, P, y.act.p, (uint16_t*)nullptr, (uint16_t*)nullptr);
-            LyGemm g2{y.act.p, 0, F, nullptr, lw.w_down, (long long)W * F, W, F, y.eo.p, 0, W, y.grp_off.p, P};
-            gemm_groups(lc, "gemm_moe_out", g2, E, P);
             const float* sh = nullptr;
-            if (d.shared_ff > 0) {
+            if (d.shared_ff > 0) {          // the always-on expert first: its split-K scratch is free again before the routed experts run
                 const int Fs = d.shared_ff;
                 gemm_tc_or_exact(c, lc, "gemm_shared_in", y.h.p, hhi, hlo, lw.s_gu, lw.tm_sgu, lw.tc_sgu, 2 * Fs, W, y.sh_gu.p, Ti);
                 launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * Fs + 255) / 256)), dim3(256), 0, (const float*)y.sh_gu.p, Fs,
@@ -585,8 +602,48 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
                 gemm_tc_or_exact(c, lc, "gemm_shared_out", y.sh_act.p, ahi, alo, lw.s_down, lw.tm_sdown, lw.tc_sdown, W, Fs, y.sh_o.p, Ti);
                 sh = y.sh_o.p;
             }
-            launch(lc, "moe_combine", 0, ly_moe_combine_kernel, dim3((W + 255) / 256, Ti), dim3(256), 0, (const float*)y.eo.p, (const int*)y.pair_of.p,
-                   (const float*)y.route_w.p, top, sh, (const float*)y.sgate.p, W, y.y.p);
+            const dim3 gw((W + 255) / 256, Ti);
+            if (lw.tc_moe && Ti > 128) {
+                // many rows: every expert over all rows on the tensor cores, kept where the row picked it (ascending expert order)
+                for (int e = 0; e < E; ++e) {
+                    dense_gemm(c, lc, "gemm_tc_moe_in", Ti, 2 * F, W, lw.tm_egu[e], y.gu.p, hhi, hlo);
+                    launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
+                           (const int*)nullptr, Ti, y.act.p, ahi, alo);
+                    dense_gemm(c, lc, "gemm_tc_moe_out", Ti, W, F, lw.tm_edown[e], y.eo.p, ahi, alo);
+                    launch(lc, "moe_accum", 0, ly_moe_accum_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.route_sel.p,
+                           (const float*)y.route_w.p, top, e, (const float*)nullptr, e == 0 ? 1 : 0, W, y.y.p);
+                }
+                if (sh != nullptr)
+                    launch(lc, "moe_accum", 0, ly_moe_accum_kernel, gw, dim3(256), 0, sh, (const int*)nullptr, (const float*)nullptr, 0, -1,
+                           (const float*)y.sgate.p, 0, W, y.y.p);
+            } else {
+                launch(lc, "moe_lists", 0, ly_moe_lists_kernel, dim3(E), dim3(32), 0, (const int*)y.route_sel.p, Ti, top, E, y.grp_off.p, y.pair_row.p,
+                       y.pair_of.p);
+                if (lw.tc_moe) {
+                    // few rows: ONE grouped GEMM pair over (expert, weight tile, k slice) items; an expert without rows costs nothing
+                    const int cap = Ti <= 16 ? 16 : (Ti <= 32 ? 32 : (Ti <= 64 ? 64 : 128));
+                    launch(lc, "moe_gather", 0, ly_moe_gather_kernel, dim3(E, std::min(Ti, 16)), dim3(256), 0, (const uint16_t*)hhi, (const uint16_t*)hlo, W,
+                           (const int*)y.grp_off.p, (const int*)y.pair_row.p, cap, y.gx_hi.p, y.gx_lo.p, y.grp_cnt.p);
+                    int ks = dense_gemm_grouped(c, lc, "gemm_tc_moe_in", E, cap, 2 * F, W, lw.tm_gu, y.gemm_out.p, y.gx_hi.p, y.gx_lo.p, y.grp_cnt.p);
+                    FL_CHECK((size_t)ks * E * cap * 2 * F <= y.gemm_out.n, FL_ERR_STATE, "internal: grouped GEMM scratch too small");
+                    launch(lc, "glu_grouped", 0, ly_glu_grouped_kernel, dim3((F + 255) / 256, E * cap), dim3(256), 0, (const float*)y.gemm_out.p, ks,
+                           (size_t)E * cap * 2 * F, F, d.limit, (const int*)y.grp_cnt.p, cap, y.ga_hi.p, y.ga_lo.p);
+                    ks = dense_gemm_grouped(c, lc, "gemm_tc_moe_out", E, cap, W, F, lw.tm_down, y.gemm_out.p, y.ga_hi.p, y.ga_lo.p, y.grp_cnt.p);
+                    FL_CHECK((size_t)ks * E * cap * W <= y.gemm_out.n, FL_ERR_STATE, "internal: grouped GEMM scratch too small");
+                    launch(lc, "moe_combine", 0, ly_moe_combine_grouped_kernel, gw, dim3(256), 0, (const float*)y.gemm_out.p, ks, (size_t)E * cap * W,
+                           (const int*)y.route_sel.p, (const int*)y.pair_of.p, (const int*)y.grp_off.p, cap, (const float*)y.route_w.p, top, sh,
+                           (const float*)y.sgate.p, W, y.y.p);
+                } else {
+                    LyGemm g1{y.h.p, 0, W, y.pair_row.p, lw.w_gu, (long long)2 * F * W, 2 * F, W, y.gu.p, 0, 2 * F, y.grp_off.p, P};
+                    gemm_groups(lc, "gemm_moe_in", g1, E, P);
+                    launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (P * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
+                           (const int*)nullptr, P, y.act.p, (uint16_t*)nullptr, (uint16_t*)nullptr);
+                    LyGemm g2{y.act.p, 0, F, nullptr, lw.w_down, (long long)W * F, W, F, y.eo.p, 0, W, y.grp_off.p, P};
+                    gemm_groups(lc, "gemm_moe_out", g2, E, P);
+                    launch(lc, "moe_combine", 0, ly_moe_combine_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.pair_of.p,
+                           (const float*)y.route_w.p, top, sh, (const float*)y.sgate.p, W, y.y.p);
+                }
+            }
         }
         launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm2b, next1, eps, W, y.h.p,
                hhi, hlo);

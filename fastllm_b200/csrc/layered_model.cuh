@@ -26,7 +26,8 @@ struct LayeredLayerW {
     int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a = 0, off_dkv = 0;             // row (= output column) offsets inside w_in
     uint16_t* w_o = nullptr;            // [W, heads * vdim]
     // GLA
-    float *a2 = nullptr, *a2b = nullptr, *hnorm = nullptr;                               // [heads*dim, rank], [heads*dim], [vdim]
+    uint16_t* a2 = nullptr;             // [heads*dim, rank]
+    float *a2b = nullptr, *hnorm = nullptr;                                              // [heads*dim], [vdim]
     // latent attention
     float* dkv_norm = nullptr;          // [kv_rank]
     uint16_t* uk_t = nullptr;           // [heads][kv_rank, dim]: W_uk per head, transposed (q absorbs it: q~ = W_uk[h]^T q)
@@ -42,6 +43,8 @@ struct LayeredLayerW {
     // serving precision: TMA descriptors of the matrices whose shapes admit the tensor-core GEMM (tc_* says which)
     CUtensorMap tm_in{}, tm_o{}, tm_gu{}, tm_down{}, tm_sgu{}, tm_sdown{};
     bool tc_in = false, tc_o = false, tc_gu = false, tc_down = false, tc_sgu = false, tc_sdown = false;
+    bool tc_moe = false;                               // experts: tm_gu / tm_down cover the stacked matrices (grouped GEMM, few rows),
+    std::vector<CUtensorMap> tm_egu, tm_edown;         //   these one expert each (every expert over all rows, many rows)
 };
 
 struct RopeSpec {                       // one distinct rotary configuration (tables are built per cache: they depend on max_seq)
@@ -96,6 +99,8 @@ struct LayeredCache {
     // serving precision: hi/lo halves of the activations that feed tensor-core GEMMs, and the split-K slices of their outputs
     DevBuf<uint16_t> h_hi, h_lo, u_hi, u_lo, act_hi, act_lo, hf_hi, hf_lo;
     DevBuf<float> gemm_out;
+    DevBuf<uint16_t> gx_hi, gx_lo, ga_hi, ga_lo;        // grouped expert GEMMs: gathered inputs / activations, [experts * cap] rows
+    DevBuf<int> grp_cnt;
 };
 
 void layered_build(LayeredModel& m, const fl_layer_desc* layers);

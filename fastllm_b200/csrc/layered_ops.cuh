@@ -194,25 +194,11 @@ static __global__ void __launch_bounds__(256) ly_gemm_kernel(LyGemm g) {
 }
 
 // ---- gated linear attention ------------------------------------------------------------------------------------------------
-// la[row, j] = log(sigmoid(a2[j, :] . a[row, :] + b[j])) / tau     (j over heads * dim key channels; a = the rank-r bottleneck)
-static __global__ void ly_gla_decay_kernel(const float* __restrict__ proj, int ldp, int off_a, int rank, const float* __restrict__ a2,
-                                           const float* __restrict__ a2b, int HD, float inv_tau, float* __restrict__ la) {
-    extern __shared__ float s_a[];
-    const int row = blockIdx.x;
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) s_a[r] = proj[(size_t)row * ldp + off_a + r];
-    __syncthreads();
-    for (int j = threadIdx.x; j < HD; j += blockDim.x) {
-        float z = a2b[j];
-        const float* w = a2 + (size_t)j * rank;
-        for (int r = 0; r < rank; ++r) z = fmaf(w[r], s_a[r], z);
-        // log sigmoid(z) = -(max(-z, 0) + log1p(exp(-|z|)))
-        la[(size_t)row * HD + j] = -(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))) * inv_tau;
-    }
-}
-
 struct GlaArgs {
     const float* proj; int ldp, off_q, off_k, off_v;
-    const float* la;            // [T, H*D] log decay
+    const float* z;             // [T, H*D] decay pre-activation W_a2 (W_a1 h), without the bias
+    const float* zb;            // [H*D] its bias
+    float inv_tau;
     float* o;                   // [T, H*Dv]
     float* state;               // [slots][H][D][Dv]
     const int *seq_row0, *seq_slot, *seq_pos0;
@@ -252,7 +238,9 @@ static __global__ void __launch_bounds__(kGlaVS * kGlaDG) ly_gla_scan_kernel(Gla
             for (int i = tid; i < D; i += blockDim.x) {
                 sq[b * D + i] = pr[a.off_q + hd * D + i] * a.qscale;
                 sk[b * D + i] = pr[a.off_k + hd * D + i];
-                sa[b * D + i] = expf(a.la[(size_t)row * a.H * D + hd * D + i]);
+                // alpha = sigmoid(z)^(1/tau) = exp(log sigmoid(z) / tau),  log sigmoid(z) = -(max(-z, 0) + log1p(exp(-|z|)))
+                const float z = a.z[(size_t)row * a.H * D + hd * D + i] + a.zb[hd * D + i];
+                sa[b * D + i] = expf(-(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))) * a.inv_tau);
             }
             if (tid < kGlaVS) sv[b * kGlaVS + tid] = (v0 + tid < Dv) ? pr[a.off_v + hd * Dv + v0 + tid] : 0.f;
         }
@@ -478,27 +466,96 @@ static __global__ void ly_router_kernel(const float* __restrict__ h, int W, cons
 }
 
 // Row lists per expert, in ascending (row, pick) order: grp_off[E + 1], pair_row[p] = source row, pair_of[row * top + k] = p.
-// One block; thread e places expert e's pairs (stable), so the lists do not depend on timing.
+// One warp per expert (grid = E blocks of 32 threads): a first sweep counts the picks of lower experts (the list's offset) and
+// its own, a second places its picks by ballot compaction -- stable, so the lists do not depend on timing.
 static __global__ void ly_moe_lists_kernel(const int* __restrict__ sel, int T, int top, int E, int* __restrict__ grp_off, int* __restrict__ pair_row,
                                            int* __restrict__ pair_of) {
-    extern __shared__ int cnt[];                 // [E + 1]
-    const int n = T * top;
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int c = 0;
-        for (int i = 0; i < n; ++i) c += sel[i] == e;
-        cnt[e] = c;
+    const int e = blockIdx.x, lane = threadIdx.x, n = T * top;
+    int less = 0, mine = 0;
+    for (int i = lane; i < n; i += 32) {
+        const int s = sel[i];
+        less += s < e;
+        mine += s == e;
     }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int run = 0;
-        for (int e = 0; e < E; ++e) { const int c = cnt[e]; cnt[e] = run; grp_off[e] = run; run += c; }
-        grp_off[E] = run;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { less += __shfl_xor_sync(0xFFFFFFFFu, less, o); mine += __shfl_xor_sync(0xFFFFFFFFu, mine, o); }
+    if (lane == 0) {
+        grp_off[e] = less;
+        if (e == E - 1) grp_off[E] = less + mine;
     }
-    __syncthreads();
-    for (int e = threadIdx.x; e < E; e += blockDim.x) {
-        int p = cnt[e];
-        for (int i = 0; i < n; ++i)
-            if (sel[i] == e) { pair_row[p] = i / top; pair_of[i] = p; ++p; }
+    int p = less;
+    for (int i0 = 0; i0 < n; i0 += 32) {
+        const int i = i0 + lane;
+        const bool hit = i < n && sel[i] == e;
+        const unsigned m = __ballot_sync(0xFFFFFFFFu, hit);
+        if (hit) {
+            const int q = p + __popc(m & ((1u << lane) - 1u));
+            pair_row[q] = i / top;
+            pair_of[i] = q;
+        }
+        p += __popc(m);
+    }
+}
+
+// ---- experts on the tensor-core GEMMs (serving precision) --------------------------------------------------------------------
+// Few rows (every expert's list fits one block of `cap` rows): block e of gx_hi / gx_lo = the hi | lo halves of the rows routed to
+// expert e, in list order; cnt[e] = their number.  grid (E, row workers).
+static __global__ void ly_moe_gather_kernel(const uint16_t* __restrict__ hhi, const uint16_t* __restrict__ hlo, int W, const int* __restrict__ grp_off,
+                                            const int* __restrict__ pair_row, int cap, uint16_t* __restrict__ gx_hi, uint16_t* __restrict__ gx_lo,
+                                            int* __restrict__ cnt) {
+    const int e = blockIdx.x, lo = grp_off[e], n = grp_off[e + 1] - lo;
+    if (blockIdx.y == 0 && threadIdx.x == 0) cnt[e] = n;
+    for (int i = blockIdx.y; i < n; i += gridDim.y) {
+        const size_t src = (size_t)pair_row[lo + i] * W, dst = ((size_t)e * cap + i) * W;
+        for (int c = threadIdx.x; c < W; c += blockDim.x) { gx_hi[dst + c] = hhi[src + c]; gx_lo[dst + c] = hlo[src + c]; }
+    }
+}
+// The clamped GLU over the grouped GEMM's output: gu[slice][e * cap + i][2F] summed over slices, rows i < cnt[e] only -> hi | lo.
+static __global__ void ly_glu_grouped_kernel(const float* __restrict__ gu, int nsl, size_t sl_stride, int F, float limit, const int* __restrict__ cnt,
+                                             int cap, uint16_t* __restrict__ ahi, uint16_t* __restrict__ alo) {
+    const int r = blockIdx.y;                   // row e * cap + i
+    if (r % cap >= cnt[r / cap]) return;
+    for (int f = blockIdx.x * blockDim.x + threadIdx.x; f < F; f += gridDim.x * blockDim.x) {
+        float g = 0.f, u = 0.f;
+        for (int k = 0; k < nsl; ++k) { g += gu[k * sl_stride + (size_t)r * 2 * F + f]; u += gu[k * sl_stride + (size_t)r * 2 * F + F + f]; }
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        split_store(ahi, alo, (size_t)r * F + f, g * sigmoidf_(1.702f * g) * (u + 1.f));
+    }
+}
+// y[row, c] = sum_k wt[row, k] * (sum over slices of eo[slice][block row of (row, k)][c]) + sgate[row] * sh[row, c]
+static __global__ void ly_moe_combine_grouped_kernel(const float* __restrict__ eo, int nsl, size_t sl_stride, const int* __restrict__ sel,
+                                                     const int* __restrict__ pair_of, const int* __restrict__ grp_off, int cap,
+                                                     const float* __restrict__ wt, int top, const float* __restrict__ sh, const float* __restrict__ sgate,
+                                                     int W, float* __restrict__ y) {
+    const int row = blockIdx.y;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < W; c += gridDim.x * blockDim.x) {
+        float t = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int e = sel[row * top + k];
+            const size_t r = (size_t)e * cap + (pair_of[row * top + k] - grp_off[e]);
+            float v = 0.f;
+            for (int sl = 0; sl < nsl; ++sl) v += eo[sl * sl_stride + r * W + c];
+            t = fmaf(wt[row * top + k], v, t);
+        }
+        if (sh != nullptr) t = fmaf(sgate[row], sh[(size_t)row * W + c], t);
+        y[(size_t)row * W + c] = t;
+    }
+}
+// Many rows: every expert runs over ALL rows on the tensor cores and a row keeps expert e's output times its routing weight (zero
+// when it did not pick e).  y (+)= w_e[row] * ye[row];  e < 0: the shared expert, weight sgate[row].  Experts in ascending order.
+static __global__ void ly_moe_accum_kernel(const float* __restrict__ ye, const int* __restrict__ sel, const float* __restrict__ wt, int top, int e,
+                                           const float* __restrict__ sgate, int first, int W, float* __restrict__ y) {
+    const int row = blockIdx.y;
+    float w = 0.f;
+    if (e < 0) w = sgate[row];
+    else
+        for (int k = 0; k < top; ++k) w += sel[row * top + k] == e ? wt[row * top + k] : 0.f;
+    if (w == 0.f && !first) return;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < W; c += gridDim.x * blockDim.x) {
+        const size_t i = (size_t)row * W + c;
+        const float add = w != 0.f ? w * ye[i] : 0.f;
+        y[i] = first ? add : y[i] + add;
     }
 }
 
