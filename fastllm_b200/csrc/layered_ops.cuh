@@ -231,41 +231,60 @@ static __global__ void __launch_bounds__(kGlaVS * kGlaDG) ly_gla_scan_kernel(Gla
         const int d = dg + kGlaDG * i;
         s[i] = (!fresh && vok && d < D) ? st[(size_t)d * Dv] : 0.f;
     }
-    int b = 0;
-    for (int row = r0; row <= r1; ++row, b ^= 1) {
-        if (row < r1) {
-            const float* pr = a.proj + (size_t)row * a.ldp;
-            for (int i = tid; i < D; i += blockDim.x) {
-                sq[b * D + i] = pr[a.off_q + hd * D + i] * a.qscale;
-                sk[b * D + i] = pr[a.off_k + hd * D + i];
-                // alpha = sigmoid(z)^(1/tau) = exp(log sigmoid(z) / tau),  log sigmoid(z) = -(max(-z, 0) + log1p(exp(-|z|)))
-                const float z = a.z[(size_t)row * a.H * D + hd * D + i] + a.zb[hd * D + i];
-                sa[b * D + i] = expf(-(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))) * a.inv_tau);
-            }
-            if (tid < kGlaVS) sv[b * kGlaVS + tid] = (v0 + tid < Dv) ? pr[a.off_v + hd * Dv + v0 + tid] : 0.f;
+    // Software pipeline: the next token's q / k / z / v travel from global memory into registers while the current token is folded
+    // into the state; they are written to the other shared-memory buffer afterwards.  One block barrier per token.
+    const bool ld_d = tid < D, ld_v = tid < kGlaVS;      // D <= 256 = blockDim: a thread fetches at most one channel of each vector
+    float rq = 0.f, rk = 0.f, rz = 0.f, rv = 0.f;
+    auto fetch = [&](int row) {
+        const float* pr = a.proj + (size_t)row * a.ldp;
+        if (ld_d) {
+            rq = pr[a.off_q + hd * D + tid];
+            rk = pr[a.off_k + hd * D + tid];
+            rz = a.z[(size_t)row * a.H * D + hd * D + tid];
         }
-        __syncthreads();
-        if (row > r0 && dg == 0 && vok) {          // finish the previous token: add the 8 partial sums in a fixed order
-            const float* rp = red + (b ^ 1) * kGlaDG * kGlaVS;
+        if (ld_v) rv = (v0 + tid < Dv) ? pr[a.off_v + hd * Dv + v0 + tid] : 0.f;
+    };
+    const float zb = ld_d ? a.zb[hd * D + tid] : 0.f;
+    auto stage = [&](int b) {
+        if (ld_d) {
+            sq[b * D + tid] = rq * a.qscale;
+            sk[b * D + tid] = rk;
+            // alpha = sigmoid(z)^(1/tau) = exp(log sigmoid(z) / tau),  log sigmoid(z) = -(max(-z, 0) + log1p(exp(-|z|)))
+            const float z = rz + zb;
+            sa[b * D + tid] = expf(-(fmaxf(-z, 0.f) + log1pf(expf(-fabsf(z)))) * a.inv_tau);
+        }
+        if (ld_v) sv[b * kGlaVS + tid] = rv;
+    };
+    auto finish = [&](int row, int b) {              // add the 8 partial sums of a token in a fixed order
+        if (dg == 0 && vok) {
+            const float* rp = red + b * kGlaDG * kGlaVS;
             float t = 0.f;
 #pragma unroll
             for (int g = 0; g < kGlaDG; ++g) t += rp[g * kGlaVS + vc];
-            a.o[(size_t)(row - 1) * a.H * Dv + hd * Dv + v0 + vc] = t;
+            a.o[(size_t)row * a.H * Dv + hd * Dv + v0 + vc] = t;
         }
-        if (row < r1) {
-            const float v = sv[b * kGlaVS + vc];
-            float acc = 0.f;
+    };
+    if (r0 < r1) { fetch(r0); stage(0); }
+    int b = 0;
+    for (int row = r0; row < r1; ++row, b ^= 1) {
+        if (row + 1 < r1) fetch(row + 1);
+        __syncthreads();
+        if (row > r0) finish(row - 1, b ^ 1);
+        const float v = sv[b * kGlaVS + vc];
+        float acc = 0.f;
 #pragma unroll
-            for (int i = 0; i < RPT; ++i) {
-                const int d = dg + kGlaDG * i;
-                if (d < D) {
-                    s[i] = fmaf(s[i], sa[b * D + d], sk[b * D + d] * v);
-                    acc = fmaf(s[i], sq[b * D + d], acc);
-                }
+        for (int i = 0; i < RPT; ++i) {
+            const int d = dg + kGlaDG * i;
+            if (d < D) {
+                s[i] = fmaf(s[i], sa[b * D + d], sk[b * D + d] * v);
+                acc = fmaf(s[i], sq[b * D + d], acc);
             }
-            red[(b * kGlaDG + dg) * kGlaVS + vc] = acc;
         }
+        red[(b * kGlaDG + dg) * kGlaVS + vc] = acc;
+        if (row + 1 < r1) stage(b ^ 1);
     }
+    __syncthreads();
+    if (r0 < r1) finish(r1 - 1, b ^ 1);
     if (vok) {
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
@@ -352,6 +371,36 @@ struct LatentAttnArgs {
     int H, D, R, C, window;
     float scale;
 };
+// CPL consecutive cache elements starting at channel c0 of a key row, as f32; channels >= C read as zero.  16-byte loads when the
+// chunk is whole, inside the latent and aligned; single elements otherwise.
+template <int CPL>
+__device__ __forceinline__ void load_chunk(const float* kp, int c0, int C, float* out) {
+    if (CPL % 4 == 0 && c0 + CPL <= C && (reinterpret_cast<uintptr_t>(kp + c0) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < CPL / 4; ++i) {
+            const float4 v = reinterpret_cast<const float4*>(kp + c0)[i];
+            out[4 * i] = v.x; out[4 * i + 1] = v.y; out[4 * i + 2] = v.z; out[4 * i + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) out[i] = c0 + i < C ? kp[c0 + i] : 0.f;
+    }
+}
+template <int CPL>
+__device__ __forceinline__ void load_chunk(const uint16_t* kp, int c0, int C, float* out) {
+    if (CPL % 8 == 0 && c0 + CPL <= C && (reinterpret_cast<uintptr_t>(kp + c0) & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < CPL / 8; ++i) {
+            const uint4 v = reinterpret_cast<const uint4*>(kp + c0)[i];
+            out[8 * i] = bf16lo(v.x); out[8 * i + 1] = bf16hi(v.x); out[8 * i + 2] = bf16lo(v.y); out[8 * i + 3] = bf16hi(v.y);
+            out[8 * i + 4] = bf16lo(v.z); out[8 * i + 5] = bf16hi(v.z); out[8 * i + 6] = bf16lo(v.w); out[8 * i + 7] = bf16hi(v.w);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) out[i] = c0 + i < C ? ld_c(kp + c0 + i) : 0.f;
+    }
+}
+
 constexpr int kLatWarps = 4;
 // One block per (row, head).  score_j = (q~ . c_j + q_rot . k_rot_j) * scale over the keys j the window admits (0 <= pos - j <
 // window), softmax in f32, out = sum_j p_j c_j.  Warp w folds keys j0 + w, j0 + w + 4, ... into an online softmax (lanes own
@@ -368,29 +417,50 @@ static __global__ void __launch_bounds__(kLatWarps * 32) ly_latent_attn_kernel(L
     const float* qap = a.qa + ((size_t)row * a.H + hd) * C;
     const float* qrp = a.proj + (size_t)row * a.ldp + a.off_q + hd * (a.D + R) + a.D;
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) { const int c = lane + 32 * i; q[i] = c < C ? qap[c] : 0.f; acc[i] = 0.f; }
+    for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; q[i] = c < C ? qap[c] : 0.f; acc[i] = 0.f; }      // a lane owns CPL consecutive channels
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) { const int c = lane + 32 * i; qr[i] = c < R ? qrp[c] : 0.f; }
+    for (int i = 0; i < RPL; ++i) { const int c = lane * RPL + i; qr[i] = c < R ? qrp[c] : 0.f; }
     float m = -INFINITY, l = 0.f;
     const int* pt = a.page_table + (size_t)slot * a.pps;
-    for (int j = j0 + wid; j <= pos; j += kLatWarps) {
-        const CT* kp = (const CT*)a.pool + ((size_t)pt[j / kKvPage] * kKvPage + j % kKvPage) * E;
-        float lat[CPL], dot = 0.f;
+    constexpr int KU = 2;                       // keys in flight per warp: their loads and reductions overlap, the folds stay in key order
+    for (int j = j0 + wid; j <= pos; j += kLatWarps * KU) {
+        float lat[KU][CPL], dot[KU];
 #pragma unroll
-        for (int i = 0; i < CPL; ++i) { const int c = lane + 32 * i; lat[i] = c < C ? ld_c(kp + c) : 0.f; dot = fmaf(q[i], lat[i], dot); }
+        for (int u = 0; u < KU; ++u) {
+            const int jj = j + u * kLatWarps;
+            dot[u] = 0.f;
+            if (jj <= pos) {
+                const CT* kp = (const CT*)a.pool + ((size_t)pt[jj / kKvPage] * kKvPage + jj % kKvPage) * E;
 #pragma unroll
-        for (int i = 0; i < RPL; ++i) { const int c = lane + 32 * i; if (c < R) dot = fmaf(qr[i], ld_c(kp + C + c), dot); }
-        const float s = warp_sum(dot) * a.scale;
-        const float mn = fmaxf(m, s), corr = expf(m - mn), p = expf(s - mn);
-        l = l * corr + p;
+                load_chunk<CPL>(kp, lane * CPL, C, lat[u]);
+                float kr[RPL];
+                load_chunk<RPL>(kp + C, lane * RPL, R, kr);
 #pragma unroll
-        for (int i = 0; i < CPL; ++i) acc[i] = acc[i] * corr + p * lat[i];
-        m = mn;
+                for (int i = 0; i < CPL; ++i) dot[u] = fmaf(q[i], lat[u][i], dot[u]);
+#pragma unroll
+                for (int i = 0; i < RPL; ++i) dot[u] = fmaf(qr[i], kr[i], dot[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) lat[u][i] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < KU; ++u) dot[u] = warp_sum(dot[u]) * a.scale;
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            if (j + u * kLatWarps > pos) break;
+            const float sc = dot[u];
+            const float mn = fmaxf(m, sc), corr = expf(m - mn), p = expf(sc - mn);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) acc[i] = acc[i] * corr + p * lat[u][i];
+            m = mn;
+        }
     }
     float* sacc = sm;
     float* sml = sm + kLatWarps * C;
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) { const int c = lane + 32 * i; if (c < C) sacc[wid * C + c] = acc[i]; }
+    for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; if (c < C) sacc[wid * C + c] = acc[i]; }
     if (lane == 0) { sml[2 * wid] = m; sml[2 * wid + 1] = l; }
     __syncthreads();
     float M = -INFINITY;
@@ -436,7 +506,16 @@ static __global__ void ly_router_kernel(const float* __restrict__ h, int W, cons
         if (e == E && wsg == nullptr) break;
         const float* w = e < E ? wr + (size_t)e * W : wsg;
         float d = 0.f;
-        for (int c = lane; c < W; c += 32) d = fmaf(w[c], hr[c], d);
+        if ((W & 3) == 0) {         // 16-byte rows: four channels per load
+            const float4* w4 = reinterpret_cast<const float4*>(w);
+            const float4* h4 = reinterpret_cast<const float4*>(hr);
+            for (int c = lane; c < W / 4; c += 32) {
+                const float4 a = w4[c], b = h4[c];
+                d = fmaf(a.x, b.x, d); d = fmaf(a.y, b.y, d); d = fmaf(a.z, b.z, d); d = fmaf(a.w, b.w, d);
+            }
+        } else {
+            for (int c = lane; c < W; c += 32) d = fmaf(w[c], hr[c], d);
+        }
         d = warp_sum(d);
         if (lane == 0) {
             if (e < E) z[e] = d; else sgate[row] = sigmoidf_(d);
