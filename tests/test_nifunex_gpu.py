@@ -155,10 +155,19 @@ def tc_cfg():
                    lat(heads=8, dim=8, rot_dim=8, vdim=8, kv_rank=32, window=25, kv_from=1, mlp=dense(ff=128))], vocab=96, width=128)
 
 
+def tc_cfg_partial_tiles():
+    """192-wide: three 64-column k blocks, weight matrices that end inside a 128-row tile (grouped experts of 384 and 192 rows),
+    five experts of which three are picked"""
+    return config([lat(heads=3, dim=48, rot_dim=16, vdim=64, kv_rank=64, window=70, mlp=moe(ff=192, experts=5, top=3, shared=(128, 1.0))),
+                   gla(heads=3, dim=64, vdim=64, rank=8, mlp=moe(ff=64, experts=2, top=2, shared=None)),
+                   lat(heads=6, dim=24, rot_dim=16, vdim=32, kv_rank=64, kv_from=0, mlp=dense(ff=320))], vocab=200, width=192)
+
+
 @pytest.mark.parametrize("dtype", ["bf16", "f32"])
-def test_tensor_core_projections(dtype):
+@pytest.mark.parametrize("make", [tc_cfg, tc_cfg_partial_tiles])
+def test_tensor_core_projections(make, dtype):
     """1 row, a few rows, up to 128 rows (weights as the 128-row operand, split-K) and more (tokens as rows) through the same layers"""
-    cfg = tc_cfg()
+    cfg = make()
     oracle, model = build(cfg, seed=21, dtype=dtype)
     toks = tokens(cfg, 333, seed=9)
     ref = oracle.run(toks)
