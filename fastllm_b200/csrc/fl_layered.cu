@@ -482,6 +482,51 @@ static void launch_gla_scan(LaunchCtx& lc, const GlaArgs& a, int n) {
     else launch(lc, "gla_scan", 0, ly_gla_scan_kernel<32>, g, b, smem, a);
 }
 
+// Latent attention of rows [r0, r0 + Ts) -- one sequence's portion, positions pos0.. -- on the tensor-core GEMM, in blocks of query
+// rows small enough that a block's score matrix stays within a fixed scratch budget.  A block only gathers the keys its rows'
+// windows reach, so long prompts with short windows never touch fully masked regions.
+static void latent_attn_tc(fl_cache& c, LaunchCtx& lc, const LayeredLayerW& lw, const LatentAttnArgs& a, int r0, int Ts, int pos0, int slot) {
+    LayeredCache& y = *c.ly;
+    const int H = a.H, C = a.C, R = a.R, E = C + R, Ep = (E + 63) / 64 * 64;
+    const size_t budget = (size_t)48 << 20;                // floats in a score block (192 MB); P halves take the same again
+    auto keys_for = [&](int qb, int first) {               // padded key count of the block of qb rows starting at local row `first`
+        const int p_lo = pos0 + first, p_hi = pos0 + std::min(Ts, first + qb);      // positions [p_lo, p_hi)
+        const int k_lo = (a.window > 0 && p_lo - a.window + 1 > 0) ? p_lo - a.window + 1 : 0;
+        return ((p_hi - k_lo) + 63) / 64 * 64;
+    };
+    int qb = 512;
+    while (qb > 8 && (size_t)qb * H * keys_for(qb, std::max(0, Ts - qb)) > budget) qb /= 2;
+    const size_t rows_max = (size_t)std::min(qb, Ts) * H;
+    size_t nkp_max = 0;
+    for (int f = 0; f < Ts; f += qb) nkp_max = std::max<size_t>(nkp_max, keys_for(qb, f));
+    auto need = [&](auto& buf, size_t n) { if (buf.n < n) { FL_CUDA(cudaStreamSynchronize(c.stream)); buf.alloc(n + n / 4); } };
+    need(y.at_kc, nkp_max * Ep); need(y.at_kct, (size_t)C * nkp_max);
+    need(y.at_qhi, rows_max * Ep); need(y.at_qlo, rows_max * Ep);
+    need(y.at_s, rows_max * nkp_max); need(y.at_phi, rows_max * nkp_max); need(y.at_plo, rows_max * nkp_max);
+    const int* page_row = y.page_table.p + (size_t)slot * c.pages_per_seq;
+    for (int f = 0; f < Ts; f += qb) {
+        const int nq = std::min(qb, Ts - f), p_lo = pos0 + f, p_hi = p_lo + nq;
+        const int k_lo = (a.window > 0 && p_lo - a.window + 1 > 0) ? p_lo - a.window + 1 : 0, nk = p_hi - k_lo, nkp = (nk + 63) / 64 * 64;
+        const int rows = nq * H;
+        if (rows <= 128) {          // a short tail: the per-(row, head) kernel
+            LatentAttnArgs t = a;
+            t.row_base = r0 + f;
+            launch_latent_attn<uint16_t>(lc, t, nq);
+            continue;
+        }
+        launch(lc, "attn_gather_keys", 0, ly_attn_gather_keys_kernel, dim3(nkp), dim3(128), 0, (const uint16_t*)a.pool, page_row, k_lo, nk, nkp, C, E, Ep,
+               y.at_kc.p, y.at_kct.p);
+        launch(lc, "attn_build_q", 0, ly_attn_build_q_kernel, dim3(nq, H), dim3(128), 0, a.qa, a.proj, a.ldp, a.off_q, r0 + f, H, a.D, R, C, Ep, a.scale,
+               y.at_qhi.p, y.at_qlo.p);
+        const CUtensorMap tk = make_tmap_bf16(y.at_kc.p, (uint64_t)nkp, (uint64_t)Ep, (uint64_t)Ep, 128);
+        dense_gemm(c, lc, "gemm_tc_attn_scores", rows, nkp, Ep, tk, y.at_s.p, y.at_qhi.p, y.at_qlo.p);
+        launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), 0, (const float*)y.at_s.p, a.row_pos, r0 + f, H, k_lo, nk, nkp, a.window,
+               y.at_phi.p, y.at_plo.p);
+        const CUtensorMap tv = make_tmap_bf16(y.at_kct.p, (uint64_t)C, (uint64_t)nkp, (uint64_t)nkp, 128);
+        dense_gemm(c, lc, "gemm_tc_attn_values", rows, C, nkp, tv, a.ol + (size_t)(r0 + f) * H * C, y.at_phi.p, y.at_plo.p);
+    }
+}
+
 void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, const uint32_t* ids, const int* want, int n_want) {
     const LayeredModel& m = *c.lm;
     LayeredCache& y = *c.ly;
@@ -567,8 +612,25 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
             LyGemm qa{y.proj.p + lw.off_q, D + R, lw.n_in, nullptr, lw.uk_t, (long long)C * D, C, D, y.qa.p, C, H * C, nullptr, Ti};
             gemm_groups(lc, "gemm_q_absorb", qa, H, Ti);
             LatentAttnArgs at{y.qa.p, y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos,
-                              st.seq_slot, y.ol.p, H, D, R, C, d.window, d.scale};
-            if (m.f32) launch_latent_attn<float>(lc, at, Ti); else launch_latent_attn<uint16_t>(lc, at, Ti);
+                              st.seq_slot, y.ol.p, H, D, R, C, d.window, d.scale, 0};
+            // long portions (serving precision): scores and weighted sums as tensor-core GEMMs over the gathered window; everything
+            // else (decoded tokens, short portions, the exact mode) on the per-(row, head) kernel.  Rows are taken in order.
+            static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
+            int done = 0;           // rows [0, done) are finished
+            for (int si = 0; si < n; ++si) {
+                const int r0 = h_row0[si], Ts = counts[si];
+                if (m.f32 || tc_attn_off || C % 8 != 0 || Ts < 64 || (long long)Ts * H <= 128) continue;
+                if (r0 > done) {
+                    at.row_base = done;
+                    launch_latent_attn<uint16_t>(lc, at, r0 - done);
+                }
+                latent_attn_tc(c, lc, lw, at, r0, Ts, h_pos0[si], slots[si]);
+                done = r0 + Ts;
+            }
+            if (done < Ti) {
+                at.row_base = done;
+                if (m.f32) launch_latent_attn<float>(lc, at, Ti - done); else launch_latent_attn<uint16_t>(lc, at, Ti - done);
+            }
             // value expansion after the softmax: out[row, h, :] = W_uv[h] (sum_j p_j c_j)
             LyGemm ov{y.ol.p, C, H * C, nullptr, lw.uv, (long long)Dv * C, Dv, C, y.u.p, Dv, H * Dv, nullptr, Ti};
             gemm_groups(lc, "gemm_v_expand", ov, H, Ti);
@@ -587,7 +649,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
         if (d.ffn == FL_FFN_DENSE) {
             gemm_tc_or_exact(c, lc, "gemm_ff_in", y.h.p, hhi, hlo, lw.w_gu, lw.tm_gu, lw.tc_gu, 2 * F, W, y.gu.p, Ti);
             launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                   (const int*)nullptr, Ti, y.act.p, lw.tc_down ? ahi : (uint16_t*)nullptr, alo);
+                   (const int*)nullptr, Ti, lw.tc_down ? (float*)nullptr : y.act.p, lw.tc_down ? ahi : (uint16_t*)nullptr, alo);
             gemm_tc_or_exact(c, lc, "gemm_ff_out", y.act.p, ahi, alo, lw.w_down, lw.tm_down, lw.tc_down, W, F, y.y.p, Ti);
         } else {
             const int E = d.experts, top = d.top, P = Ti * top;
@@ -598,7 +660,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
                 const int Fs = d.shared_ff;
                 gemm_tc_or_exact(c, lc, "gemm_shared_in", y.h.p, hhi, hlo, lw.s_gu, lw.tm_sgu, lw.tc_sgu, 2 * Fs, W, y.sh_gu.p, Ti);
                 launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * Fs + 255) / 256)), dim3(256), 0, (const float*)y.sh_gu.p, Fs,
-                       d.shared_limit, (const int*)nullptr, Ti, y.sh_act.p, lw.tc_sdown ? ahi : (uint16_t*)nullptr, alo);
+                       d.shared_limit, (const int*)nullptr, Ti, lw.tc_sdown ? (float*)nullptr : y.sh_act.p, lw.tc_sdown ? ahi : (uint16_t*)nullptr, alo);
                 gemm_tc_or_exact(c, lc, "gemm_shared_out", y.sh_act.p, ahi, alo, lw.s_down, lw.tm_sdown, lw.tc_sdown, W, Fs, y.sh_o.p, Ti);
                 sh = y.sh_o.p;
             }
@@ -608,7 +670,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
                 for (int e = 0; e < E; ++e) {
                     dense_gemm(c, lc, "gemm_tc_moe_in", Ti, 2 * F, W, lw.tm_egu[e], y.gu.p, hhi, hlo);
                     launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                           (const int*)nullptr, Ti, y.act.p, ahi, alo);
+                           (const int*)nullptr, Ti, (float*)nullptr, ahi, alo);
                     dense_gemm(c, lc, "gemm_tc_moe_out", Ti, W, F, lw.tm_edown[e], y.eo.p, ahi, alo);
                     launch(lc, "moe_accum", 0, ly_moe_accum_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.route_sel.p,
                            (const float*)y.route_w.p, top, e, (const float*)nullptr, e == 0 ? 1 : 0, W, y.y.p);

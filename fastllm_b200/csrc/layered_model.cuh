@@ -101,6 +101,9 @@ struct LayeredCache {
     DevBuf<float> gemm_out;
     DevBuf<uint16_t> gx_hi, gx_lo, ga_hi, ga_lo;        // grouped expert GEMMs: gathered inputs / activations, [experts * cap] rows
     DevBuf<int> grp_cnt;
+    // tensor-core latent attention of long portions: gathered keys, their transpose, Q / P operand halves, the score block
+    DevBuf<uint16_t> at_kc, at_kct, at_qhi, at_qlo, at_phi, at_plo;
+    DevBuf<float> at_s;
 };
 
 void layered_build(LayeredModel& m, const fl_layer_desc* layers);

@@ -370,6 +370,7 @@ struct LatentAttnArgs {
     float* ol;                  // [T, H, C] softmax-weighted sum of latents
     int H, D, R, C, window;
     float scale;
+    int row_base;               // first row of this launch (blockIdx.x counts from it)
 };
 // CPL consecutive cache elements starting at channel c0 of a key row, as f32; channels >= C read as zero.  16-byte loads when the
 // chunk is whole, inside the latent and aligned; single elements otherwise.
@@ -401,15 +402,15 @@ __device__ __forceinline__ void load_chunk(const uint16_t* kp, int c0, int C, fl
     }
 }
 
-constexpr int kLatWarps = 4;
+constexpr int kLatWarps = 8;
 // One block per (row, head).  score_j = (q~ . c_j + q_rot . k_rot_j) * scale over the keys j the window admits (0 <= pos - j <
-// window), softmax in f32, out = sum_j p_j c_j.  Warp w folds keys j0 + w, j0 + w + 4, ... into an online softmax (lanes own
-// channels); the four partial results are merged at the end.  Which warp takes which key depends on the position alone.
+// window), softmax in f32, out = sum_j p_j c_j.  Warp w of the eight folds keys j0 + w, j0 + w + 8, ... into an online softmax (lanes own
+// channels); the eight partial results are merged at the end.  Which warp takes which key depends on the position alone.
 template <typename CT, int CPL>
 static __global__ void __launch_bounds__(kLatWarps * 32) ly_latent_attn_kernel(LatentAttnArgs a) {
     extern __shared__ float sm[];               // [kLatWarps][C] accumulators, then [kLatWarps][2] (max, sum)
     constexpr int RPL = 4;                      // rotated channels per lane (R <= 128)
-    const int row = blockIdx.x, hd = blockIdx.y, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int row = a.row_base + blockIdx.x, hd = blockIdx.y, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int C = a.C, R = a.R, E = C + R;
     const int pos = a.row_pos[row], slot = a.seq_slot[a.row_seq[row]];
     const int j0 = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
@@ -479,6 +480,67 @@ static __global__ void __launch_bounds__(kLatWarps * 32) ly_latent_attn_kernel(L
     }
 }
 
+// ---- latent attention for long portions on the tensor-core GEMM (serving precision) ---------------------------------------------
+// A block of consecutive query rows of ONE sequence and the keys its window can reach [k_lo, k_lo + nk):
+//   S = Q~ . Kc^T (one GEMM: rows = (token, head) pairs -- every head of a token meets the same latent keys),
+//   P = masked softmax(S) in f32,   O = P . Kc[:, :C] (a second GEMM against the transposed latents).
+// Kc [nkp, Ep]: the keys' cache rows (latent | rotated part | zero padding), KcT [C, nkp]: the latents transposed; padding is
+// zero so that masked probabilities (exact zeros) meet finite values.
+static __global__ void ly_attn_gather_keys_kernel(const uint16_t* __restrict__ pool, const int* __restrict__ page_row, int k_lo, int nk, int nkp, int C,
+                                                  int E, int Ep, uint16_t* __restrict__ kc, uint16_t* __restrict__ kct) {
+    const int r = blockIdx.x;
+    const uint16_t* src = nullptr;
+    if (r < nk) {
+        const int j = k_lo + r;
+        src = pool + ((size_t)page_row[j / kKvPage] * kKvPage + j % kKvPage) * E;
+    }
+    for (int c = threadIdx.x; c < Ep; c += blockDim.x) {
+        const uint16_t v = (src != nullptr && c < E) ? src[c] : (uint16_t)0;
+        kc[(size_t)r * Ep + c] = v;
+        if (c < C) kct[(size_t)c * nkp + r] = v;
+    }
+}
+// Q operand rows (token, head): [q~ * scale | rotated query part * scale | 0] as hi | lo halves
+static __global__ void ly_attn_build_q_kernel(const float* __restrict__ qa, const float* __restrict__ proj, int ldp, int off_q, int row0, int H, int D,
+                                              int R, int C, int Ep, float scale, uint16_t* __restrict__ qhi, uint16_t* __restrict__ qlo) {
+    const int t = blockIdx.x, hd = blockIdx.y, row = row0 + t;
+    const float* qap = qa + ((size_t)row * H + hd) * C;
+    const float* qrp = proj + (size_t)row * ldp + off_q + hd * (D + R) + D;
+    const size_t base = ((size_t)t * H + hd) * Ep;
+    for (int c = threadIdx.x; c < Ep; c += blockDim.x) {
+        const float v = c < C ? qap[c] * scale : (c < C + R ? qrp[c - C] * scale : 0.f);
+        split_store(qhi, qlo, base + c, v);
+    }
+}
+// P[r, col] = softmax over the keys the row's position admits (0 <= pos - j < window, j = k_lo + col), zero elsewhere; r = (token, head)
+static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const int* __restrict__ row_pos, int row0, int H, int k_lo, int nk, int nkp,
+                                              int window, uint16_t* __restrict__ phi, uint16_t* __restrict__ plo) {
+    __shared__ float red[33];
+    const size_t r = blockIdx.x;
+    const int pos = row_pos[row0 + (int)(r / H)];
+    const int j_first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+    const int c_lo = j_first > k_lo ? j_first - k_lo : 0, c_hi = min(nk, pos - k_lo + 1);      // visible columns [c_lo, c_hi)
+    const float* sr = S + r * nkp;
+    float m = -INFINITY;
+    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) m = fmaxf(m, sr[c]);
+    m = warp_max(m);
+    {
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+        __syncthreads();
+        if (lane == 0) red[wid] = m;
+        __syncthreads();
+        float t = lane < nw ? red[lane] : -INFINITY;
+        m = warp_max(t);
+    }
+    float sum = 0.f;
+    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) sum += expf(sr[c] - m);
+    const float inv = 1.f / block_sum(sum, red);
+    for (int c = threadIdx.x; c < nkp; c += blockDim.x) {
+        const float p = (c >= c_lo && c < c_hi) ? expf(sr[c] - m) * inv : 0.f;
+        split_store(phi, plo, r * nkp + c, p);
+    }
+}
+
 // ---- feed-forward ----------------------------------------------------------------------------------------------------------
 // act[p, f] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[p, f], limit),  u = clamp(gu[p, F + f], -limit, limit);  p < *count
 static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float limit, const int* __restrict__ count, int rows, float* __restrict__ act,
@@ -490,7 +552,7 @@ static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float 
         const float g = fminf(gu[p * 2 * F + f], limit);
         const float u = fminf(fmaxf(gu[p * 2 * F + F + f], -limit), limit);
         const float v = g * sigmoidf_(1.702f * g) * (u + 1.f);
-        act[i] = v;
+        if (act != nullptr) act[i] = v;         // nullptr: only the hi | lo halves are consumed (a tensor-core GEMM follows)
         split_store(ahi, alo, i, v);
     }
 }
