@@ -88,7 +88,7 @@ static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, 
     }
 }
 
-// x[row] += norm(y[row]; wb);  then, if wnext, h[row] = norm(x[row]; wnext)      (norm: weight stored around zero)
+// x[row] += norm(y[row]; wb);  then, if wnext, h[row] = norm(x[row]; wnext)      (norm: zero-centred weight: the scale is 1 + w)
 static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
                                            const float* __restrict__ wnext, float eps, int W, float* __restrict__ h, uint16_t* __restrict__ hhi,
                                            uint16_t* __restrict__ hlo) {

@@ -100,7 +100,7 @@ typedef struct fl_config {
 } fl_config;
 
 /* ---- layered models: every layer names its own mixer and feed-forward (no reference counterpart) ----------------------------
- * A layer is  x += norm_b(mixer(norm_a(x)));  x += norm_d(ffn(norm_c(x)))  with RMS norms whose weight is stored around zero
+ * A layer is  x += norm_b(mixer(norm_a(x)));  x += norm_d(ffn(norm_c(x)))  with RMS norms with a zero-centred weight
  * (x / sqrt(mean x^2 + eps) * (1 + w)).  Mixers:
  *   FL_MIXER_GLA          gated linear attention: per head a [dim, vdim] f32 state S <- diag(alpha) S + k v^T, o = S^T q with a
  *                         per-key-channel decay alpha = sigmoid(W_a2 W_a1 h + b)^(1/tau) through a rank-`decay_rank` bottleneck;

@@ -18,7 +18,7 @@ def rms(x, eps):
 
 
 def norm_offset(x, w, eps):
-    """the layer norms and the final norm: weight stored around zero"""
+    """the layer norms and the final norm: zero-centred weight: the scale is 1 + w"""
     return rms(x, eps) * (1.0 + w)
 
 
