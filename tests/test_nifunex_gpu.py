@@ -384,3 +384,53 @@ def test_checkpoint_folder_through_the_registry(tmp_path):
     assert isinstance(model, models.NifunexWithConfig)
     toks = tokens(cfg, 30)
     assert relerr(run_whole(model, toks), O.Nifunex(cfg, w).run(toks)) < TOL["f32"]
+
+
+def test_trace_runner_end_to_end(tmp_path):
+    """bin/trace_run as a process: a checkpoint folder, steps on standard input (portions beside single tokens, a request that
+    sits out a step, one that wants nothing, a fifth request that takes over a finished one's slot and pages), logits files out"""
+    import json
+    import os
+    import subprocess
+    from fastllm_b200 import safetensors_io
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = hybrid_cfg(window=30)
+    w = O.random_weights(cfg, 23)
+    file_cfg = json.loads(json.dumps(cfg))
+    for l in file_cfg["layers"]:
+        l["mixer"].pop("decay_rank", None)
+    model_dir, out_dir = tmp_path / "model", tmp_path / "out"
+    model_dir.mkdir()
+    (model_dir / "config.json").write_text(json.dumps(file_cfg))
+    safetensors_io.write_safetensors(str(model_dir / "model.safetensors"), {k: to_bits(v) for k, v in w.items()})
+    oracle = O.Nifunex(cfg, w)
+    reqs = {name: tokens(cfg, n, seed=50 + i) for i, (name, n) in enumerate((("a", 70), ("b", 5), ("c", 33), ("d", 64), ("e", 40)))}
+    ref = {k: oracle.run(v) for k, v in reqs.items()}
+    plan = [[("a", 3, [0, 2]), ("b", 1, [0])],
+            [("a", 60, [59]), ("c", 33, []), ("d", 2, [1])],
+            [("b", 4, [0, 3]), ("d", 62, [0, 61])],                       # a sits this step out; b, c and d end here
+            [("a", 1, [0]), ("e", 40, [39])],                             # e arrives after three requests left
+            [("a", 6, [0, 5])]]
+    at = {k: 0 for k in reqs}
+    lines, expect = [], {}
+    for n, step in enumerate(plan):
+        entries, rows, end = [], [], []
+        for rid, cnt, want in step:
+            entries.append({"id": rid, "tokens": reqs[rid][at[rid]:at[rid] + cnt], "want": want})
+            rows += [ref[rid][at[rid] + p] for p in want]
+            at[rid] += cnt
+            if at[rid] == len(reqs[rid]):
+                end.append(rid)
+        lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
+        expect[n] = np.stack(rows) if rows else None
+    assert all(at[k] == len(reqs[k]) for k in reqs)
+    for dtype, tol in (("float32", TOL["f32"]), ("bfloat16", TOL["bf16"])):
+        p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out", str(out_dir), "--max-tokens", "256"],
+                           input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == ["done %d" % n for n in range(len(plan))]
+        for n, want in expect.items():
+            f = out_dir / ("%d.f32" % n)
+            got = np.fromfile(f, dtype="<f4").reshape(-1, cfg["vocab"])
+            assert got.shape == want.shape and relerr(got, want) < tol
+            f.unlink()
