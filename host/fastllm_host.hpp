@@ -284,6 +284,137 @@ struct ContinuousBatcher {
     }
 };
 
+// ---- layered decoder (no reference path): per-layer mixers / feed-forward described by fl_layer_desc -----------------------------
+// The host parses config.json with its own JSON library into fl_stack_config + one fl_layer_desc per layer (field for field what
+// fastllm_b200/models.py nifunex_layer_descs does; the decay bottleneck's rows are the first dimension of the 'l<i>.mix.a1'
+// tensor), hands the tensors over by name and drives a pooled cache through mixed steps.
+struct LayeredModel {
+    fl_model* h = nullptr;
+    fl_stack_config cfg{};
+    std::vector<fl_layer_desc> layers;
+    LayeredModel(const fl_stack_config& c, std::vector<fl_layer_desc> l, const TensorMap& tensors) : cfg(c), layers(std::move(l)) {
+        cfg.n_layers = (int32_t)layers.size();
+        check(fl_model_create_layered(&cfg, layers.data(), &h));
+        for (const auto& kv : tensors)
+            check(fl_model_put_tensor(h, kv.first.c_str(), kv.second.dtype, kv.second.shape.data(), (int)kv.second.shape.size(), kv.second.data));
+        check(fl_model_finalize(h));
+    }
+    LayeredModel(const fl_stack_config& c, std::vector<fl_layer_desc> l, uint64_t seed, float std_dev) : cfg(c), layers(std::move(l)) {   // synthetic weights
+        cfg.n_layers = (int32_t)layers.size();
+        check(fl_model_create_layered(&cfg, layers.data(), &h));
+        check(fl_model_random_init(h, seed, std_dev));
+        check(fl_model_finalize(h));
+    }
+    ~LayeredModel() { if (h) fl_model_destroy(h); }
+    LayeredModel(const LayeredModel&) = delete;
+    LayeredModel& operator=(const LayeredModel&) = delete;
+};
+
+// Pooled cache of a layered model: `max_slots` sequences share ceil(pool_tokens / 64) pages; every sequence also owns the
+// recurrent-state slot of the model's stateful layers.
+struct PooledCache {
+    fl_cache* h = nullptr;
+    int vocab = 0;
+    PooledCache(const LayeredModel& m, int max_slots, int max_seq, int pool_tokens) : vocab(m.cfg.vocab) {
+        check(fl_cache_create_pooled(m.h, max_slots, max_seq, pool_tokens, &h));
+    }
+    ~PooledCache() { if (h) fl_cache_destroy(h); }
+    PooledCache(const PooledCache&) = delete;
+    PooledCache& operator=(const PooledCache&) = delete;
+    // One mixed step: sequence i (slot slots[i]) is fed portions[i]; want[i] lists the places inside that portion whose logits are
+    // asked for.  -> f32 [sum of wanted places, vocab], sequence-major.
+    std::vector<float> forward_ragged(const LayeredModel& m, const std::vector<int>& slots, const std::vector<std::vector<uint32_t>>& portions,
+                                      const std::vector<std::vector<int>>& want) {
+        std::vector<int> counts, rows;
+        std::vector<uint32_t> ids;
+        for (size_t i = 0; i < portions.size(); ++i) {
+            for (int p : want[i]) rows.push_back((int)ids.size() + p);
+            counts.push_back((int)portions[i].size());
+            ids.insert(ids.end(), portions[i].begin(), portions[i].end());
+        }
+        std::vector<float> out(rows.size() * (size_t)vocab);
+        check(fl_forward_ragged(m.h, h, slots.data(), counts.data(), (int)slots.size(), ids.data(), rows.data(), (int)rows.size(), out.data()));
+        return out;
+    }
+    void slot_reset(int slot) { check(fl_cache_slot_reset(h, slot)); }
+    std::pair<int, int> pool_stats() const {
+        int total = 0, free_pages = 0;
+        check(fl_cache_pool_stats(h, &total, &free_pages));
+        return {total, free_pages};
+    }
+};
+
+// Mixed-step scheduler (transliteration of models.py ContinuousBatcher._generate_mixed): a request takes a free slot as soon as
+// there is one; every step carries, per running request, the next portion of its prompt (at most prefill_chunk tokens) or its one
+// new token; sampling, EOS and the token budget as in Model::generate; a finished request gives its slot back.
+struct MixedBatcher {
+    const LayeredModel& model;
+    int max_batch, prefill_chunk;
+    std::optional<uint32_t> eos_token_id;
+    PooledCache cache;
+    int steps = 0;
+    MixedBatcher(const LayeredModel& m, int max_batch_, int prefill_chunk_, std::optional<uint32_t> eos = std::nullopt, int max_seq = kKvCapacity)
+        : model(m), max_batch(max_batch_), prefill_chunk(prefill_chunk_), eos_token_id(eos), cache(m, max_batch_, max_seq, max_batch_ * max_seq) {}
+
+    std::vector<std::vector<uint32_t>> generate(const std::vector<std::vector<uint32_t>>& prompts, int max_tokens, float temperature = 0.0f) {
+        struct Running { size_t req; size_t fed; std::unique_ptr<LogitsProcessor> lp; uint32_t tok; };
+        std::vector<std::vector<uint32_t>> out(prompts.size());
+        if (max_tokens <= 0) return out;
+        std::vector<size_t> waiting;
+        for (size_t i = prompts.size(); i-- > 0;) waiting.push_back(i);
+        std::vector<int> free_slots;
+        for (int s = max_batch; s-- > 0;) free_slots.push_back(s);
+        std::map<int, Running> running;
+        const size_t V = (size_t)model.cfg.vocab;
+        while (!waiting.empty() || !running.empty()) {
+            while (!waiting.empty() && !free_slots.empty()) {
+                running[free_slots.back()] = Running{waiting.back(), 0, std::make_unique<LogitsProcessor>(0, (double)temperature), 0};
+                free_slots.pop_back(); waiting.pop_back();
+            }
+            std::vector<int> slots;
+            std::vector<std::vector<uint32_t>> portions;
+            std::vector<std::vector<int>> want;
+            for (auto& kv : running) {                                   // ascending slots
+                Running& st = kv.second;
+                const std::vector<uint32_t>& p = prompts[st.req];
+                slots.push_back(kv.first);
+                if (st.fed < p.size()) {
+                    const size_t n = std::min(p.size() - st.fed, (size_t)prefill_chunk);
+                    portions.emplace_back(p.begin() + st.fed, p.begin() + st.fed + n);
+                    st.fed += n;
+                    want.push_back(st.fed == p.size() ? std::vector<int>{(int)n - 1} : std::vector<int>{});
+                } else {
+                    portions.push_back({st.tok});
+                    want.push_back({0});
+                }
+            }
+            const std::vector<float> logits = cache.forward_ragged(model, slots, portions, want);
+            steps += 1;
+            size_t row = 0;
+            for (size_t i = 0; i < slots.size(); ++i) {
+                if (want[i].empty()) continue;
+                Running& st = running[slots[i]];
+                const uint32_t tok = st.lp->sample(logits.data() + row * V, V);
+                row += 1;
+                bool done;
+                if (eos_token_id && tok == *eos_token_id) {
+                    done = true;
+                } else {
+                    out[st.req].push_back(tok);
+                    st.tok = tok;
+                    done = (int)out[st.req].size() >= max_tokens;
+                }
+                if (done) {
+                    running.erase(slots[i]);
+                    cache.slot_reset(slots[i]);
+                    free_slots.push_back(slots[i]);
+                }
+            }
+        }
+        return out;
+    }
+};
+
 // ---- EmbeddingModel (models/embeddings.rs:17-38) / MiniLMModel (:245-447) after tokenisation -------------------------------------
 struct BertConfig {   // models/embeddings.rs:46-54 (+ the vocabulary size the reference takes from the tokenizer, :301-306)
     int hidden_size = 384, num_attention_heads = 12, num_hidden_layers = 6, intermediate_size = 1536, max_position_embeddings = 512;

@@ -29,6 +29,43 @@ int main(int argc, char** argv) {
             return 1;
         }
     }
+    if (argc > 5 && std::strcmp(argv[1], "--layered") == 0) {
+        // host_selftest --layered max_tokens max_batch prefill_chunk id id / id id id / ...: a two-layer synthetic layered decoder
+        // (gated linear attention + dense feed-forward, windowed latent attention + experts) through the C++ MixedBatcher, exact mode
+        try {
+            const int max_tokens = std::atoi(argv[2]), max_batch = std::atoi(argv[3]), chunk = std::atoi(argv[4]);
+            std::vector<std::vector<uint32_t>> prompts(1);
+            for (int i = 5; i < argc; ++i) {
+                if (std::strcmp(argv[i], "/") == 0) prompts.emplace_back();
+                else prompts.back().push_back((uint32_t)std::strtoul(argv[i], nullptr, 10));
+            }
+            fastllm::check(fl_init(0));
+            fl_stack_config sc{};
+            sc.arch = FL_ARCH_NIFUNEX; sc.vocab = 48; sc.width = 32; sc.norm_eps = 1e-5f; sc.compute_dtype = FL_DTYPE_F32;
+            std::vector<fl_layer_desc> ly(2);
+            ly[0].mixer = FL_MIXER_GLA; ly[0].heads = 2; ly[0].dim = 8; ly[0].vdim = 8; ly[0].decay_rank = 4; ly[0].tau = 8.0f; ly[0].kv_from = -1;
+            ly[0].ffn = FL_FFN_DENSE; ly[0].ff = 24; ly[0].limit = 1.5f;
+            ly[1].mixer = FL_MIXER_LATENT_ATTN; ly[1].heads = 2; ly[1].dim = 8; ly[1].vdim = 8; ly[1].rot_dim = 4; ly[1].kv_rank = 16; ly[1].kv_from = -1;
+            ly[1].window = 9; ly[1].rot_dims = 4; ly[1].rot_base = 10000.0; ly[1].scale = 0.28867513f;
+            ly[1].ffn = FL_FFN_MOE; ly[1].ff = 16; ly[1].limit = 1.0f; ly[1].experts = 4; ly[1].top = 2; ly[1].shared_ff = 24; ly[1].shared_limit = 0.75f;
+            fastllm::LayeredModel model(sc, ly, /*seed=*/5, /*std=*/0.3f);
+            fastllm::MixedBatcher mb(model, max_batch, chunk, std::nullopt, 256);
+            const auto outs = mb.generate(prompts, max_tokens);
+            std::printf("[");
+            for (size_t r = 0; r < outs.size(); ++r) {
+                std::printf("%s[", r ? "," : "");
+                for (size_t i = 0; i < outs[r].size(); ++i) std::printf("%s%u", i ? "," : "", outs[r][i]);
+                std::printf("]");
+            }
+            std::printf("]\n");
+            const auto ps = mb.cache.pool_stats();
+            std::fprintf(stderr, "mixed steps: %d, pool %d/%d free\n", mb.steps, ps.second, ps.first);
+            return ps.first == ps.second ? 0 : 1;
+        } catch (const std::exception& e) {
+            std::fprintf(stderr, "host_selftest --layered failed: %s\n", e.what());
+            return 1;
+        }
+    }
     // argv: weights.bin (concatenated f32 tensors in manifest order), manifest.txt (name ndim dims...), prompt ids...
     if (argc < 4) { std::fprintf(stderr, "usage: host_selftest manifest.txt weights.bin max_tokens id...\n"); return 2; }
     try {

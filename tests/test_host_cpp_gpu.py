@@ -60,3 +60,26 @@ def test_cpp_continuous_batcher_equals_the_python_mirror(tmp_path):
     model, _ = product_model(cfg, w)
     want = models.ContinuousBatcher(model, max_batch=2, eos_token_id=None).generate(prompts, 5)
     assert json.loads(out.stdout.strip().splitlines()[0]) == want
+
+
+@pytest.mark.gpu
+def test_cpp_mixed_batcher_equals_the_python_mirror():
+    """The layered decoder through host/fastllm_host.hpp (LayeredModel, PooledCache, MixedBatcher) and through models.py: the same
+    synthetic weights (device-side generator, same seed), the same mixed steps, identical ids."""
+    from fastllm_b200 import models
+    cfg = {"architecture": "Nifunex", "vocab": 48, "width": 32, "norm": {"eps": 1e-5}, "layers": [
+        {"type": "gla", "mixer": {"heads": 2, "dim": 8, "vdim": 8, "tau": 8.0}, "mlp": {"kind": "dense", "ff": 24, "limit": 1.5}},
+        {"type": "latent_attention", "mixer": {"heads": 2, "dim": 8, "rot_dim": 4, "vdim": 8, "kv_rank": 16, "scale": 0.28867513, "mask": {"size": 9},
+                                                "rot": {"base": 10000.0, "dims": 4}},
+         "mlp": {"kind": "moe", "expert": {"ff": 16, "limit": 1.0}, "router": {"experts": 4, "top": 2}, "shared": {"ff": 24, "limit": 0.75}}}]}
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, 48, n).tolist() for n in (11, 2, 37, 5)]
+    args = []
+    for i, p in enumerate(prompts):
+        args += (["/"] if i else []) + [str(t) for t in p]
+    out = subprocess.run([EXE, "--layered", "9", "2", "8"] + args, capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    model, _ = models.NifunexWithConfig.initialize_model(cfg, None, "f32", random_seed=5, std=0.3, decay_rank=4)
+    want = models.ContinuousBatcher(model, max_batch=2, eos_token_id=None, prefill_chunk=8).generate(prompts, 9)
+    assert json.loads(out.stdout.strip().splitlines()[0]) == want
+    assert any(len(set(ids)) > 1 for ids in want)          # the synthetic model does not collapse to one token
