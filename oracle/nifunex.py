@@ -77,9 +77,12 @@ def rotate_pairs(x, pos, freqs, mult, dims):
 
 # ---- the model -------------------------------------------------------------------------------------------------------
 class Nifunex:
-    """weights: dict name -> float array (already holding the values the product sees, e.g. bf16-rounded)."""
+    """weights: dict name -> float array (already holding the values the product sees, e.g. bf16-rounded).
+    cache_round: optional function applied to what a latent-attention layer caches (latent and rotated key part) -- bf16_round
+    restates a cache kept in bfloat16, so that a serving-precision run can be held to a tight bar."""
 
-    def __init__(self, config: dict, weights: dict):
+    def __init__(self, config: dict, weights: dict, cache_round=None):
+        self.cache_round = cache_round
         self.cfg = config
         self.w = {k: np.asarray(v, dtype=np.float64) for k, v in weights.items()}
         self.eps = float(config["norm"]["eps"])
@@ -124,6 +127,8 @@ class Nifunex:
             ckv = w[p + "dkv"] @ h
             lat = norm_plain(ckv[:C], w[p + "dkv.norm"], self.eps)
             krot = rotate_pairs(ckv[C:], pos, freqs, mult, m["rot"]["dims"])
+            if self.cache_round is not None:
+                lat, krot = np.asarray(self.cache_round(lat), dtype=np.float64), np.asarray(self.cache_round(krot), dtype=np.float64)
             st["kv"][i].append((lat, krot))
             src = i
         hist = st["kv"][src]

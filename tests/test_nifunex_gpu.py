@@ -2,7 +2,10 @@
 
 Small random configurations of the tests' own (never a shipped model's sizes); the product runs through the C ABI
 (models.NifunexWithConfig / DeviceCache.forward_ragged), the oracle token by token in float64.  Two precisions: "f32" (every
-product and the cache in 32-bit) is held to a tight bar, "bf16" (the serving precision) to the rounding of a bf16 cache.
+product and the cache in 32-bit) against the exact oracle; "bf16" (the serving precision: tensor-core GEMMs over hi | lo activation
+halves, bf16 latent cache) against the oracle that rounds what it caches to bf16.  What is left between the two in that mode is
+the occasional cached element that lands on the other side of a bf16 rounding boundary (f32 against f64 arithmetic: one element
+moves by 2^-8 of its value and the logits near it by ~1e-3), hence the wider bar there.
 """
 import numpy as np
 import pytest
@@ -13,7 +16,7 @@ from oracle import nifunex as O
 
 pytestmark = pytest.mark.gpu
 
-TOL = {"f32": 4e-5, "bf16": 3e-2}
+TOL = {"f32": 4e-5, "bf16": 1e-2}
 
 
 # ---- configurations ---------------------------------------------------------------------------------------------------------
@@ -71,14 +74,14 @@ def build(cfg, seed=0, dtype="f32", tweak=None):
         if tweak:
             tweak(w)
         model, _ = models.NifunexWithConfig.initialize_model(cfg, {k: to_bits(v) for k, v in w.items()}, dtype)
-        _built[key] = (O.Nifunex(cfg, w), model)
+        _built[key] = (O.Nifunex(cfg, w, cache_round=O.bf16_round if dtype == "bf16" else None), model)
     return _built[key]
 
 
 def relerr(got, ref, allow=0.0):
     """worst position's error: rms over the vocabulary of the logits' difference (means taken off) relative to the rms of the
-    logits.  allow: share of positions left out, worst first -- the serving precision keeps the latent cache in bf16, and a
-    2e-3 change upstream of a random router flips a near-tied expert pick now and then (the exact mode never needs this)."""
+    logits.  allow: share of positions left out, worst first (long serving-precision runs only: a 1e-3 change upstream of a random
+    router can flip a near-tied expert pick; the exact mode never needs it)."""
     d = np.asarray(got, dtype=np.float64) - ref
     d = d - d.mean(-1, keepdims=True)
     r = ref - ref.mean(-1, keepdims=True)
@@ -403,33 +406,34 @@ def test_trace_runner_end_to_end(tmp_path):
     model_dir.mkdir()
     (model_dir / "config.json").write_text(json.dumps(file_cfg))
     safetensors_io.write_safetensors(str(model_dir / "model.safetensors"), {k: to_bits(v) for k, v in w.items()})
-    oracle = O.Nifunex(cfg, w)
     reqs = {name: tokens(cfg, n, seed=50 + i) for i, (name, n) in enumerate((("a", 70), ("b", 5), ("c", 33), ("d", 64), ("e", 40)))}
-    ref = {k: oracle.run(v) for k, v in reqs.items()}
+    refs = {"float32": {k: O.Nifunex(cfg, w).run(v) for k, v in reqs.items()},
+            "bfloat16": {k: O.Nifunex(cfg, w, cache_round=O.bf16_round).run(v) for k, v in reqs.items()}}
     plan = [[("a", 3, [0, 2]), ("b", 1, [0])],
             [("a", 60, [59]), ("c", 33, []), ("d", 2, [1])],
             [("b", 4, [0, 3]), ("d", 62, [0, 61])],                       # a sits this step out; b, c and d end here
             [("a", 1, [0]), ("e", 40, [39])],                             # e arrives after three requests left
             [("a", 6, [0, 5])]]
     at = {k: 0 for k in reqs}
-    lines, expect = [], {}
+    lines, places = [], {}
     for n, step in enumerate(plan):
         entries, rows, end = [], [], []
         for rid, cnt, want in step:
             entries.append({"id": rid, "tokens": reqs[rid][at[rid]:at[rid] + cnt], "want": want})
-            rows += [ref[rid][at[rid] + p] for p in want]
+            rows += [(rid, at[rid] + p) for p in want]
             at[rid] += cnt
             if at[rid] == len(reqs[rid]):
                 end.append(rid)
         lines.append(json.dumps({"step": n, "entries": entries, "end": end}))
-        expect[n] = np.stack(rows) if rows else None
+        places[n] = rows
     assert all(at[k] == len(reqs[k]) for k in reqs)
     for dtype, tol in (("float32", TOL["f32"]), ("bfloat16", TOL["bf16"])):
         p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(model_dir), "--dtype", dtype, "--out", str(out_dir), "--max-tokens", "256"],
                            input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=600)
         assert p.returncode == 0, p.stderr[-2000:]
         assert [l for l in p.stdout.splitlines() if l.startswith("done ")] == ["done %d" % n for n in range(len(plan))]
-        for n, want in expect.items():
+        for n, rows in places.items():
+            want = np.stack([refs[dtype][rid][p] for rid, p in rows])
             f = out_dir / ("%d.f32" % n)
             got = np.fromfile(f, dtype="<f4").reshape(-1, cfg["vocab"])
             assert got.shape == want.shape and relerr(got, want) < tol
