@@ -378,11 +378,19 @@ void layered_cache_reset(fl_cache& c) {
     for (int s = 0; s < c.max_batch; ++s) layered_slot_reset(c, s);
 }
 
+// captured decode steps hold workspace pointers: they go when a buffer they name is reallocated
+static void drop_graphs(fl_cache& c) {
+    for (auto& kv : c.graphs)
+        if (kv.second.exec) cudaGraphExecDestroy(kv.second.exec);
+    c.graphs.clear();
+}
+
 static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
     const LayeredModel& m = *c.lm;
     LayeredCache& y = *c.ly;
     if (T > y.rows) {
         FL_CUDA(cudaStreamSynchronize(c.stream));
+        drop_graphs(c);
         const size_t R = std::max<size_t>(T, 2 * y.rows), W = m.W, P = R * std::max(m.max_top, 1);
         y.x.alloc(R * W); y.h.alloc(R * W); y.y.alloc(R * W);
         y.proj.alloc(R * m.max_in); y.u.alloc(R * std::max(m.max_hv, 1)); y.go.alloc(R * std::max(m.max_hv, 1));
@@ -420,6 +428,7 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
     }
     if (n_want > y.want_cap) {
         FL_CUDA(cudaStreamSynchronize(c.stream));
+        drop_graphs(c);
         const size_t N = std::max<size_t>(n_want, 2 * y.want_cap);
         y.hf.alloc(N * m.W); y.logits.alloc(N * m.V); y.h_logits.alloc(N * m.V);
         if (!m.f32) { y.hf_hi.alloc(N * m.W); y.hf_lo.alloc(N * m.W); }
@@ -527,6 +536,9 @@ static void latent_attn_tc(fl_cache& c, LaunchCtx& lc, const LayeredLayerW& lw, 
     }
 }
 
+static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const int* slots, const int* counts, int n, const int* h_row0,
+                         const int* h_pos0);
+
 void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, const uint32_t* ids, const int* want, int n_want) {
     const LayeredModel& m = *c.lm;
     LayeredCache& y = *c.ly;
@@ -554,6 +566,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
     const size_t tab_ints = (size_t)3 * T + 3 * (size_t)n + 1 + (size_t)n_want;
     if (tab_ints > y.tab_cap) {
         FL_CUDA(cudaStreamSynchronize(c.stream));
+        drop_graphs(c);
         y.tab_cap = std::max(tab_ints, 2 * y.tab_cap);
         y.step_tab.alloc(y.tab_cap); y.h_step_tab.alloc(y.tab_cap);
     }
@@ -582,7 +595,53 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
     LaunchCtx lc;
     lc.stream = c.stream;
     lc.pdl = false;
-    const int Ti = (int)T, W = m.W;
+    // A step in which every sequence brings ONE token has a launch geometry that depends on (sequences, wanted rows) alone --
+    // positions, slots and pages are read from the device tables -- so it is captured into a CUDA graph the second time the pair is
+    // seen and replayed from then on (FL_NO_GRAPH=1 keeps eager launches).
+    static const bool no_graph = env_flag("FL_NO_GRAPH");
+    if (T == n && !g_prof.on && !no_graph) {
+        const GraphKey key{n, 1000 + n_want};
+        auto it = c.graphs.find(key);
+        if (it == c.graphs.end()) {
+            c.graphs[key] = GraphEntry{};               // first sight: run eagerly (one-time kernel attributes, lazy loading)
+            enqueue_step(c, lc, st, slots, counts, n, h_row0, h_pos0);
+        } else {
+            if (it->second.exec == nullptr) {
+                lc.capturing = true;
+                cudaGraph_t graph = nullptr;
+                FL_CUDA(cudaStreamBeginCapture(c.stream, cudaStreamCaptureModeThreadLocal));
+                try {
+                    enqueue_step(c, lc, st, slots, counts, n, h_row0, h_pos0);
+                } catch (...) {
+                    cudaStreamEndCapture(c.stream, &graph);
+                    if (graph) cudaGraphDestroy(graph);
+                    throw;
+                }
+                FL_CUDA(cudaStreamEndCapture(c.stream, &graph));
+                GraphEntry e;
+                FL_CUDA(cudaGraphInstantiate(&e.exec, graph, 0));
+                FL_CUDA(cudaGraphDestroy(graph));
+                e.kernels = lc.captured;
+                it->second = e;
+            }
+            FL_CUDA(cudaGraphLaunch(it->second.exec, c.stream));
+            g_launches.fetch_add(it->second.kernels, std::memory_order_relaxed);
+        }
+    } else {
+        enqueue_step(c, lc, st, slots, counts, n, h_row0, h_pos0);
+    }
+    if (n_want > 0)
+        FL_CUDA(cudaMemcpyAsync(y.h_logits.p, y.logits.p, (size_t)n_want * m.V * 4, cudaMemcpyDeviceToHost, c.stream));
+    for (int i = 0; i < n; ++i) c.slot_len[slots[i]] += counts[i];
+}
+
+// The device part of a step: every layer over all rows, then the vocabulary projection of the wanted rows.
+static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const int* slots, const int* counts, int n, const int* h_row0,
+                         const int* h_pos0) {
+    const LayeredModel& m = *c.lm;
+    LayeredCache& y = *c.ly;
+    const int n_want = st.n_want;
+    const int Ti = st.T, W = m.W;
     const float eps = m.cfg.norm_eps;
     const int nthr = std::min(1024, std::max(64, (W + 31) / 32 * 32));
     uint16_t *hhi = m.f32 ? nullptr : y.h_hi.p, *hlo = m.f32 ? nullptr : y.h_lo.p, *uhi = m.f32 ? nullptr : y.u_hi.p, *ulo = m.f32 ? nullptr : y.u_lo.p,
@@ -714,9 +773,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
         launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, y.hf.p,
                m.tc_head ? y.hf_hi.p : (uint16_t*)nullptr, y.hf_lo.p);
         gemm_tc_or_exact(c, lc, "gemm_head", y.hf.p, m.tc_head ? y.hf_hi.p : nullptr, y.hf_lo.p, m.head, m.tm_head, m.tc_head, m.V, W, y.logits.p, n_want);
-        FL_CUDA(cudaMemcpyAsync(y.h_logits.p, y.logits.p, (size_t)n_want * m.V * 4, cudaMemcpyDeviceToHost, c.stream));
     }
-    for (int i = 0; i < n; ++i) c.slot_len[slots[i]] += counts[i];
 }
 
 }  // namespace fl
