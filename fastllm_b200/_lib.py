@@ -11,8 +11,9 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libfastllm_b200.so")
 
-FL_ARCH = {"llama": 0, "mistral": 1, "qwen2": 2, "mixtral": 3, "bert": 4, "nifunex": 5}
-FL_MIXER = {"gla": 0, "latent_attention": 1}
+FL_ARCH = {"llama": 0, "mistral": 1, "qwen2": 2, "mixtral": 3, "bert": 4, "nifunex": 5, "rofetar": 6}
+FL_MIXER = {"gla": 0, "latent_attention": 1, "attention": 2, "mamba2": 3, "delta": 4}
+FL_ACT = {"swish_clamp": 0, "gelu_tanh": 1}
 FL_FFN = {"none": 0, "dense": 1, "moe": 2}
 FL_DTYPE_F32, FL_DTYPE_BF16, FL_DTYPE_F16 = 0, 1, 2
 
@@ -33,12 +34,14 @@ class FlLayerDesc(C.Structure):
                 ("rot_dims", C.c_int32), ("rot_base", C.c_double), ("scale", C.c_float), ("yarn_factor", C.c_float),
                 ("yarn_original", C.c_float), ("yarn_fast", C.c_float), ("yarn_slow", C.c_float), ("ffn", C.c_int32), ("ff", C.c_int32),
                 ("limit", C.c_float), ("experts", C.c_int32), ("top", C.c_int32), ("shared_ff", C.c_int32), ("shared_limit", C.c_float),
-                ("reserved", C.c_int32 * 4)]
+                ("kv_heads", C.c_int32), ("conv", C.c_int32), ("state", C.c_int32), ("groups", C.c_int32), ("norm_groups", C.c_int32),
+                ("softcap", C.c_float), ("sink", C.c_int32), ("rot_halves", C.c_int32), ("ffn_act", C.c_int32), ("ffn_bias", C.c_int32),
+                ("reserved", C.c_int32 * 6)]
 
 
 class FlStackConfig(C.Structure):
     _fields_ = [("arch", C.c_int32), ("vocab", C.c_int32), ("width", C.c_int32), ("n_layers", C.c_int32), ("norm_eps", C.c_float),
-                ("compute_dtype", C.c_int32), ("reserved", C.c_int32 * 6)]
+                ("compute_dtype", C.c_int32), ("norm_plain", C.c_int32), ("no_pre_norm", C.c_int32), ("reserved", C.c_int32 * 4)]
 
 
 class FastllmError(RuntimeError):

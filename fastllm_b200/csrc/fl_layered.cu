@@ -1,5 +1,5 @@
-// Layered decoder (FL_ARCH_NIFUNEX): weight layout + ingest, pooled cache (latent pages + recurrent-state slots), and the
-// step function for mixed batches (portions of prompts beside single decoded tokens).
+// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR): weight layout + ingest, pooled cache (pages of latents or keys | values +
+// recurrent-state slots), and the step function for mixed batches (portions of prompts beside single decoded tokens).
 #include <cmath>
 #include <map>
 
@@ -45,7 +45,7 @@ static std::mutex g_routes_mu;
 
 static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
     const std::string at = "layer " + std::to_string(i) + ": ";
-    FL_CHECK(d.heads >= 1 && d.dim >= 1 && d.vdim >= 1, FL_ERR_INVALID, at + "heads / dim / vdim must be positive");
+    FL_CHECK(d.heads >= 1 && (d.dim >= 1 || d.mixer == FL_MIXER_MAMBA2) && d.vdim >= 1, FL_ERR_INVALID, at + "heads / dim / vdim must be positive");
     if (d.mixer == FL_MIXER_GLA) {
         FL_CHECK(d.decay_rank >= 1 && d.decay_rank <= 4096 && d.tau > 0.f, FL_ERR_INVALID, at + "bad decay rank / tau");
         FL_CHECK(d.dim <= 256, FL_ERR_UNSUPPORTED, at + "gated linear attention: at most 256 key channels per head");
@@ -62,9 +62,35 @@ static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
                          s.yarn_original == d.yarn_original && s.yarn_fast == d.yarn_fast && s.yarn_slow == d.yarn_slow,
                      FL_ERR_INVALID, at + "kv_from must name a latent-attention layer with its own cache and the same latent / rotary sizes");
         }
+    } else if (d.mixer == FL_MIXER_ATTN) {
+        const int G = d.kv_heads > 0 ? d.kv_heads : d.heads;
+        FL_CHECK(d.heads % G == 0, FL_ERR_INVALID, at + "heads must be a multiple of kv_heads");
+        FL_CHECK(d.dim <= 256 && d.vdim <= 256, FL_ERR_UNSUPPORTED, at + "attention: at most 256 channels per head");
+        FL_CHECK(d.rot_dims >= 0 && d.rot_dims <= d.dim && d.rot_dims % 2 == 0, FL_ERR_INVALID, at + "rotated channels must be even and <= dim");
+        FL_CHECK(d.window >= 0 && d.softcap >= 0.f, FL_ERR_INVALID, at + "negative window / score cap");
+        if (d.kv_from >= 0) {
+            FL_CHECK(d.kv_from < i, FL_ERR_INVALID, at + "kv_from must name an earlier layer");
+            const fl_layer_desc& s = m.layers[d.kv_from].d;
+            const int Gs = s.kv_heads > 0 ? s.kv_heads : s.heads;
+            FL_CHECK(s.mixer == FL_MIXER_ATTN && s.kv_from < 0 && Gs == G && s.dim == d.dim && s.vdim == d.vdim, FL_ERR_INVALID,
+                     at + "kv_from must name an attention layer with its own cache and the same key / value head sizes");
+        }
+    } else if (d.mixer == FL_MIXER_MAMBA2) {
+        FL_CHECK(d.state >= 1 && d.state <= 256, FL_ERR_UNSUPPORTED, at + "Mamba-2: state size must be in 1..256");
+        FL_CHECK(d.groups >= 1 && d.heads % d.groups == 0, FL_ERR_INVALID, at + "heads must be a multiple of groups");
+        FL_CHECK(d.norm_groups >= 1 && (d.heads * d.vdim) % d.norm_groups == 0, FL_ERR_INVALID, at + "the inner width must divide into norm_groups parts");
+        FL_CHECK(d.conv >= 1 && d.conv <= kMaxTaps, FL_ERR_UNSUPPORTED, at + "convolution taps must be in 1..16");
+    } else if (d.mixer == FL_MIXER_DELTA) {
+        const int G = d.kv_heads > 0 ? d.kv_heads : d.heads;
+        FL_CHECK(d.heads % G == 0, FL_ERR_INVALID, at + "heads must be a multiple of kv_heads");
+        FL_CHECK(d.dim <= 256, FL_ERR_UNSUPPORTED, at + "delta rule: at most 256 key channels per head");
+        FL_CHECK(d.conv >= 1 && d.conv <= kMaxTaps, FL_ERR_UNSUPPORTED, at + "convolution taps must be in 1..16");
     } else {
         FL_CHECK(false, FL_ERR_INVALID, at + "unknown mixer");
     }
+    FL_CHECK(d.ffn_act == FL_ACT_SWISH_CLAMP || d.ffn_act == FL_ACT_GELU_TANH, FL_ERR_INVALID, at + "unknown feed-forward activation");
+    FL_CHECK(d.ffn != FL_FFN_MOE || (d.ffn_act == FL_ACT_SWISH_CLAMP && !d.ffn_bias), FL_ERR_UNSUPPORTED,
+             at + "experts use the clamped activation without biases");
     if (d.ffn == FL_FFN_DENSE) {
         FL_CHECK(d.ff >= 1, FL_ERR_INVALID, at + "ff must be positive");
     } else if (d.ffn == FL_FFN_MOE) {
@@ -77,7 +103,7 @@ static void check_layer(const LayeredModel& m, int i, const fl_layer_desc& d) {
 
 void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
     const fl_stack_config& c = m.cfg;
-    FL_CHECK(c.arch == FL_ARCH_NIFUNEX, FL_ERR_INVALID, "layered models: unknown arch");
+    FL_CHECK(c.arch == FL_ARCH_NIFUNEX || c.arch == FL_ARCH_ROFETAR, FL_ERR_INVALID, "layered models: unknown arch");
     FL_CHECK(c.vocab >= 1 && c.width >= 1 && c.n_layers >= 1 && c.n_layers <= 4096, FL_ERR_INVALID, "layered models: sizes must be positive");
     FL_CHECK(c.compute_dtype == FL_DTYPE_BF16 || c.compute_dtype == FL_DTYPE_F32, FL_ERR_INVALID, "compute_dtype must be bf16 or f32");
     m.W = c.width; m.V = c.vocab; m.L = c.n_layers; m.f32 = c.compute_dtype == FL_DTYPE_F32;
@@ -93,8 +119,59 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         const fl_layer_desc& d = lw.d;
         check_layer(m, i, d);
         const size_t H = d.heads, D = d.dim, Dv = d.vdim;
-        reg(&lw.norm1, W * 4); reg(&lw.norm1b, W * 4);
-        if (d.mixer == FL_MIXER_GLA) {
+        const bool pre = !c.no_pre_norm;
+        if (pre) reg(&lw.norm1, W * 4);
+        reg(&lw.norm1b, W * 4);
+        auto pad8 = [](int n) { return (n + 7) / 8 * 8; };
+        auto recurrent = [&](size_t rows) {            // a per-slot state [heads][rows][vdim] + the per-head decay parameters
+            lw.gla_index = (int)m.gla_layers.size();
+            m.gla_layers.push_back(i);
+            (void)rows;
+            m.max_heads = std::max<int>(m.max_heads, (int)H);
+        };
+        if (d.mixer == FL_MIXER_ATTN) {
+            if (lw.d.kv_heads <= 0) lw.d.kv_heads = lw.d.heads;
+            const size_t G = lw.d.kv_heads;
+            lw.off_q = 0; lw.n_in = (int)(H * D); lw.off_k = lw.off_v = -1;
+            reg(&lw.qnorm, D * 4);
+            if (d.kv_from < 0) {
+                lw.off_k = lw.n_in; lw.off_v = lw.off_k + (int)(G * D); lw.n_in = lw.off_v + (int)(G * Dv);
+                reg(&lw.knorm, D * 4);
+                lw.kv_owner = i;
+                lw.kv_index = (int)m.kv_layers.size();
+                m.kv_layers.push_back(i);
+            } else {
+                lw.kv_owner = d.kv_from;
+                lw.kv_index = m.layers[d.kv_from].kv_index;
+            }
+            lw.n_in = pad8(lw.n_in);
+            const RopeSpec rs{d.rot_dims, d.rot_base, d.yarn_factor, d.yarn_original, d.yarn_fast, d.yarn_slow};
+            int ri = -1;
+            for (size_t k = 0; k < m.ropes.size(); ++k)
+                if (m.ropes[k] == rs) ri = (int)k;
+            if (ri < 0) { ri = (int)m.ropes.size(); m.ropes.push_back(rs); }
+            lw.rope_index = ri;
+        } else if (d.mixer == FL_MIXER_MAMBA2) {
+            const size_t inner = H * Dv, GN = (size_t)d.groups * d.state;
+            lw.off_g = 0;                               // z, the output gate
+            lw.off_v = (int)inner; lw.off_k = (int)(2 * inner); lw.off_q = (int)(2 * inner + GN);    // x | B | C
+            lw.off_dt = (int)(2 * inner + 2 * GN);
+            lw.n_in = pad8(lw.off_dt + (int)H);
+            lw.conv_off = (int)inner; lw.conv_ch = (int)(inner + 2 * GN);
+            reg(&lw.conv_w, (size_t)lw.conv_ch * d.conv * 4); reg(&lw.conv_b, (size_t)lw.conv_ch * 4);
+            reg(&lw.a_log, H * 4); reg(&lw.dt_bias, H * 4); reg(&lw.dskip, H * 4); reg(&lw.hnorm, inner * 4);
+            recurrent(d.state);
+        } else if (d.mixer == FL_MIXER_DELTA) {
+            if (lw.d.kv_heads <= 0) lw.d.kv_heads = lw.d.heads;
+            const size_t G = lw.d.kv_heads;
+            lw.off_q = 0; lw.off_k = (int)(G * D); lw.off_v = (int)(2 * G * D); lw.off_g = lw.off_v + (int)(H * Dv);
+            lw.off_b = lw.off_g + (int)(H * Dv); lw.off_a = lw.off_b + (int)H;
+            lw.n_in = pad8(lw.off_a + (int)H);
+            lw.conv_off = 0; lw.conv_ch = lw.off_g;
+            reg(&lw.conv_w, (size_t)lw.conv_ch * d.conv * 4);
+            reg(&lw.a_log, H * 4); reg(&lw.dt_bias, H * 4); reg(&lw.hnorm, Dv * 4);
+            recurrent(D);
+        } else if (d.mixer == FL_MIXER_GLA) {
             lw.off_q = 0; lw.off_k = (int)(H * D); lw.off_v = (int)(2 * H * D); lw.off_g = lw.off_v + (int)(H * Dv);
             lw.off_a = lw.off_g + (int)(H * Dv);
             lw.n_in = lw.off_a + d.decay_rank;
@@ -129,8 +206,11 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         reg(&lw.w_o, W * H * Dv * 2);
         m.max_in = std::max(m.max_in, lw.n_in);
         m.max_hv = std::max<int>(m.max_hv, (int)(H * Dv));
+        m.max_cv = std::max(m.max_cv, lw.conv_ch);
         if (d.ffn != FL_FFN_NONE) {
-            reg(&lw.norm2, W * 4); reg(&lw.norm2b, W * 4);
+            if (pre) reg(&lw.norm2, W * 4);
+            reg(&lw.norm2b, W * 4);
+            if (d.ffn == FL_FFN_DENSE && d.ffn_bias) { reg(&lw.b_gu, (size_t)2 * d.ff * 4); reg(&lw.b_down, W * 4); }
             const size_t G = d.ffn == FL_FFN_MOE ? d.experts : 1, F = d.ff;
             reg(&lw.w_gu, G * 2 * F * W * 2); reg(&lw.w_down, G * W * F * 2);
             m.max_ff = std::max<int>(m.max_ff, (int)F);
@@ -165,8 +245,31 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         const fl_layer_desc& d = lw.d;
         const std::string p = "l" + std::to_string(i) + ".";
         const int64_t H = d.heads, D = d.dim, Dv = d.vdim;
-        vec(p + "norm1", lw.norm1, W, 1); vec(p + "norm1b", lw.norm1b, W, 1);
-        if (d.mixer == FL_MIXER_GLA) {
+        const bool pre = !c.no_pre_norm;
+        if (pre) { vec(p + "norm1", lw.norm1, W, 1); vec(p + "norm1b", lw.norm1b, W, 1); }
+        else vec(p + "norm1", lw.norm1b, W, 1);
+        if (d.mixer == FL_MIXER_ATTN) {
+            const int64_t G = d.kv_heads;
+            mat(p + "mix.q", lw.w_in, lw.off_q, H * D, W); vec(p + "mix.q.norm", lw.qnorm, D, 1);
+            if (d.kv_from < 0) {
+                mat(p + "mix.k", lw.w_in, lw.off_k, G * D, W); mat(p + "mix.v", lw.w_in, lw.off_v, G * Dv, W);
+                vec(p + "mix.k.norm", lw.knorm, D, 1);
+            }
+        } else if (d.mixer == FL_MIXER_MAMBA2) {
+            mat(p + "mix.in", lw.w_in, 0, lw.off_dt + H, W);
+            vec(p + "mix.conv", lw.conv_w, lw.conv_ch, d.conv); vec(p + "mix.conv.b", lw.conv_b, lw.conv_ch, 1);
+            vec(p + "mix.dt_bias", lw.dt_bias, H, 1); vec(p + "mix.A_log", lw.a_log, H, 1); vec(p + "mix.D", lw.dskip, H, 1);
+            vec(p + "mix.norm", lw.hnorm, H * Dv, 1);
+        } else if (d.mixer == FL_MIXER_DELTA) {
+            const int64_t G = d.kv_heads;
+            mat(p + "mix.q", lw.w_in, lw.off_q, G * D, W); mat(p + "mix.k", lw.w_in, lw.off_k, G * D, W);
+            mat(p + "mix.v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "mix.g", lw.w_in, lw.off_g, H * Dv, W);
+            mat(p + "mix.b", lw.w_in, lw.off_b, H, W); mat(p + "mix.a", lw.w_in, lw.off_a, H, W);
+            vec(p + "mix.q.conv", lw.conv_w + (size_t)lw.off_q * d.conv, G * D, d.conv);
+            vec(p + "mix.k.conv", lw.conv_w + (size_t)lw.off_k * d.conv, G * D, d.conv);
+            vec(p + "mix.v.conv", lw.conv_w + (size_t)lw.off_v * d.conv, H * Dv, d.conv);
+            vec(p + "mix.A_log", lw.a_log, H, 1); vec(p + "mix.dt_bias", lw.dt_bias, H, 1); vec(p + "mix.norm", lw.hnorm, Dv, 1);
+        } else if (d.mixer == FL_MIXER_GLA) {
             mat(p + "mix.q", lw.w_in, lw.off_q, H * D, W); mat(p + "mix.k", lw.w_in, lw.off_k, H * D, W);
             mat(p + "mix.v", lw.w_in, lw.off_v, H * Dv, W); mat(p + "mix.g", lw.w_in, lw.off_g, H * Dv, W);
             mat(p + "mix.a1", lw.w_in, lw.off_a, d.decay_rank, W);
@@ -180,10 +283,14 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
         }
         mat(p + "mix.o", lw.w_o, 0, W, H * Dv);
         if (d.ffn == FL_FFN_NONE) continue;
-        vec(p + "norm2", lw.norm2, W, 1); vec(p + "norm2b", lw.norm2b, W, 1);
+        if (pre) { vec(p + "norm2", lw.norm2, W, 1); vec(p + "norm2b", lw.norm2b, W, 1); }
+        else vec(p + "norm2", lw.norm2b, W, 1);
         const int64_t F = d.ff;
         if (d.ffn == FL_FFN_DENSE) {
             mat(p + "mlp.gate", lw.w_gu, 0, F, W); mat(p + "mlp.up", lw.w_gu, F, F, W); mat(p + "mlp.down", lw.w_down, 0, W, F);
+            if (d.ffn_bias) {
+                vec(p + "mlp.gate.b", lw.b_gu, F, 1); vec(p + "mlp.up.b", lw.b_gu + F, F, 1); vec(p + "mlp.down.b", lw.b_down, W, 1);
+            }
         } else {
             vec(p + "mlp.router", lw.router, d.experts, W);
             for (int e = 0; e < d.experts; ++e) {
@@ -249,8 +356,12 @@ void layered_random_init(LayeredModel& m, uint64_t seed, float stdv) {
         const uint64_t ts = tensor_seed(seed, n.c_str());
         const int64_t numel = r->rows * r->cols;
         if (r->kind == LyRoute::F32) {
-            const bool around_one = n.size() >= 8 && (n.compare(n.size() - 8, 8, "mix.norm") == 0 || n.compare(n.size() - 8, 8, "dkv.norm") == 0);
-            const bool is_mat = n.find("router") != std::string::npos || n.find("mix.a2") != std::string::npos || n.find("shared.sg") != std::string::npos;
+            auto ends = [&](const char* t) { const size_t k = std::strlen(t); return n.size() >= k && n.compare(n.size() - k, k, t) == 0; };
+            // a plain norm weight sits around one, a zero-centred one around zero
+            const bool around_one = ends("mix.norm") || ends("dkv.norm") || ends("q.norm") || ends("k.norm") || ends("mix.D") ||
+                                    (m.cfg.norm_plain && (ends("norm1") || ends("norm2") || ends("norm1b") || ends("norm2b") || n == "final.norm"));
+            const bool is_mat = n.find("router") != std::string::npos || n.find("mix.a2") != std::string::npos || n.find("shared.sg") != std::string::npos ||
+                                ends(".conv");
             const bool is_bias = n.size() >= 4 && n.compare(n.size() - 4, 4, "a2.b") == 0;
             if (around_one) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 1.0f);
             else if (is_bias) fill_f32_kernel<<<8, 256>>>((float*)r->dst, numel, 3.0f);
@@ -346,13 +457,18 @@ void layered_cache_create(fl_cache& c, int max_slots, int max_seq, int pool_toke
     y.kv_store.resize(m.kv_layers.size());
     for (size_t k = 0; k < m.kv_layers.size(); ++k) {
         const fl_layer_desc& d = m.layers[m.kv_layers[k]].d;
-        y.kv_store[k].alloc((size_t)pages * kKvPage * (d.kv_rank + d.rot_dim) * esz, true);
+        const size_t width = d.mixer == FL_MIXER_ATTN ? (size_t)d.kv_heads * (d.dim + d.vdim) : (size_t)(d.kv_rank + d.rot_dim);
+        y.kv_store[k].alloc((size_t)pages * kKvPage * width * esz, true);
         y.kv_pool.push_back(y.kv_store[k].p);
     }
     y.gla_state.resize(m.gla_layers.size());
+    y.conv_state.resize(m.gla_layers.size());
     for (size_t k = 0; k < m.gla_layers.size(); ++k) {
-        const fl_layer_desc& d = m.layers[m.gla_layers[k]].d;
-        y.gla_state[k].alloc((size_t)max_slots * d.heads * d.dim * d.vdim, true);
+        const LayeredLayerW& lw = m.layers[m.gla_layers[k]];
+        const fl_layer_desc& d = lw.d;
+        const size_t rows = d.mixer == FL_MIXER_MAMBA2 ? d.state : d.dim;
+        y.gla_state[k].alloc((size_t)max_slots * d.heads * rows * d.vdim, true);
+        if (lw.conv_ch > 0 && d.conv > 1) y.conv_state[k].alloc((size_t)max_slots * (d.conv - 1) * lw.conv_ch, true);
     }
     y.rope_cos.resize(m.ropes.size()); y.rope_sin.resize(m.ropes.size());
     for (size_t k = 0; k < m.ropes.size(); ++k) {
@@ -395,6 +511,7 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
         y.x.alloc(R * W); y.h.alloc(R * W); y.y.alloc(R * W);
         y.proj.alloc(R * m.max_in); y.u.alloc(R * std::max(m.max_hv, 1)); y.go.alloc(R * std::max(m.max_hv, 1));
         y.la.alloc(R * std::max(m.max_hd, 1));
+        y.cv.alloc(R * std::max(m.max_cv, 1)); y.rs.alloc(R * 2 * std::max(m.max_heads, 1));
         y.qa.alloc(R * std::max(m.max_hc, 1)); y.ol.alloc(R * std::max(m.max_hc, 1));
         y.gu.alloc(P * 2 * std::max(m.max_ff, 1)); y.act.alloc(P * std::max(m.max_ff, 1)); y.eo.alloc(P * W);
         y.sh_gu.alloc(R * 2 * std::max(m.max_ff, 1)); y.sh_act.alloc(R * std::max(m.max_ff, 1)); y.sh_o.alloc(R * W);
@@ -489,6 +606,32 @@ static void launch_gla_scan(LaunchCtx& lc, const GlaArgs& a, int n) {
     else if (rpt <= 8) launch(lc, "gla_scan", 0, ly_gla_scan_kernel<8>, g, b, smem, a);
     else if (rpt <= 16) launch(lc, "gla_scan", 0, ly_gla_scan_kernel<16>, g, b, smem, a);
     else launch(lc, "gla_scan", 0, ly_gla_scan_kernel<32>, g, b, smem, a);
+}
+
+template <typename CT>
+static void launch_gqa_attn(LaunchCtx& lc, const GqaAttnArgs& a, int T) {
+    if (T <= 0) return;
+    const int cpl = (std::max(a.D, a.Dv) + 31) / 32;
+    const size_t smem = ((size_t)kGqaWarps * a.Dv + 2 * kGqaWarps) * 4;
+    const dim3 g(T, a.H), b(kGqaWarps * 32);
+    if (cpl <= 1) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 1>, g, b, smem, a);
+    else if (cpl <= 2) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 2>, g, b, smem, a);
+    else if (cpl <= 4) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 4>, g, b, smem, a);
+    else launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 8>, g, b, smem, a);
+}
+
+template <bool DELTA>
+static void launch_rec_scan(LaunchCtx& lc, const RecArgs& a, int n) {
+    const int rpt = (a.D + kGlaDG - 1) / kGlaDG;
+    const size_t smem = ((size_t)4 * a.D + 2 * kGlaVS + 4 + 3 * kGlaDG * kGlaVS) * 4;
+    const dim3 g(n, a.H, (a.Dv + kGlaVS - 1) / kGlaVS), b(kGlaVS * kGlaDG);
+    const char* tag = DELTA ? "delta_scan" : "ssm_scan";
+    if (rpt <= 1) launch(lc, tag, 0, ly_rec_scan_kernel<1, DELTA>, g, b, smem, a);
+    else if (rpt <= 2) launch(lc, tag, 0, ly_rec_scan_kernel<2, DELTA>, g, b, smem, a);
+    else if (rpt <= 4) launch(lc, tag, 0, ly_rec_scan_kernel<4, DELTA>, g, b, smem, a);
+    else if (rpt <= 8) launch(lc, tag, 0, ly_rec_scan_kernel<8, DELTA>, g, b, smem, a);
+    else if (rpt <= 16) launch(lc, tag, 0, ly_rec_scan_kernel<16, DELTA>, g, b, smem, a);
+    else launch(lc, tag, 0, ly_rec_scan_kernel<32, DELTA>, g, b, smem, a);
 }
 
 // Latent attention of rows [r0, r0 + Ts) -- one sequence's portion, positions pos0.. -- on the tensor-core GEMM, in blocks of query
@@ -646,14 +789,58 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
     const int nthr = std::min(1024, std::max(64, (W + 31) / 32 * 32));
     uint16_t *hhi = m.f32 ? nullptr : y.h_hi.p, *hlo = m.f32 ? nullptr : y.h_lo.p, *uhi = m.f32 ? nullptr : y.u_hi.p, *ulo = m.f32 ? nullptr : y.u_lo.p,
              *ahi = m.f32 ? nullptr : y.act_hi.p, *alo = m.f32 ? nullptr : y.act_lo.p;
-    launch(lc, "embed_norm", 0, ly_embed_norm_kernel, dim3(Ti), dim3(nthr), 0, (const uint16_t*)m.embed, st.tok, W, (const float*)m.layers[0].norm1, eps,
-           y.x.p, y.h.p, hhi, hlo);
+    // pre-norm stacks: a sublayer reads h = norm(x) (written by the kernel that last touched x); otherwise it reads x itself and
+    // the same kernel writes x's hi | lo halves for the tensor-core GEMMs
+    const bool pre = !m.cfg.no_pre_norm;
+    const int plain = m.cfg.norm_plain ? 1 : 0, split_x = pre ? 0 : 1;
+    const float* sub_in = pre ? y.h.p : y.x.p;
+    launch(lc, "embed_norm", 0, ly_embed_norm_kernel, dim3(Ti), dim3(nthr), 0, (const uint16_t*)m.embed, st.tok, W,
+           pre ? (const float*)m.layers[0].norm1 : (const float*)nullptr, eps, plain, y.x.p, y.h.p, hhi, hlo);
     for (int li = 0; li < m.L; ++li) {
         const LayeredLayerW& lw = m.layers[li];
         const fl_layer_desc& d = lw.d;
         const int H = d.heads, D = d.dim, Dv = d.vdim;
-        gemm_tc_or_exact(c, lc, "gemm_mix_in", y.h.p, hhi, hlo, lw.w_in, lw.tm_in, lw.tc_in, lw.n_in, W, y.proj.p, Ti);
-        if (d.mixer == FL_MIXER_GLA) {
+        gemm_tc_or_exact(c, lc, "gemm_mix_in", sub_in, hhi, hlo, lw.w_in, lw.tm_in, lw.tc_in, lw.n_in, W, y.proj.p, Ti);
+        if (d.mixer == FL_MIXER_ATTN) {
+            const int G = d.kv_heads;
+            AttnPrepArgs pa{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, lw.qnorm, lw.knorm, eps, y.kv_pool[lw.kv_index], y.page_table.p,
+                            c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot, y.rope_cos[lw.rope_index].p, y.rope_sin[lw.rope_index].p,
+                            H, G, D, Dv, d.rot_dims, d.rot_halves};
+            const size_t psm = (size_t)4 * D * 4;
+            if (m.f32) launch(lc, "attn_prep", 0, ly_attn_prep_kernel<float>, dim3(Ti), dim3(128), psm, pa);
+            else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti), dim3(128), psm, pa);
+            GqaAttnArgs at{y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot,
+                           y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0};
+            if (m.f32) launch_gqa_attn<float>(lc, at, Ti); else launch_gqa_attn<uint16_t>(lc, at, Ti);
+        } else if (d.mixer == FL_MIXER_MAMBA2 || d.mixer == FL_MIXER_DELTA) {
+            const bool delta = d.mixer == FL_MIXER_DELTA;
+            const int G = delta ? d.kv_heads : d.groups, rows = delta ? D : d.state;
+            float* cstate = d.conv > 1 ? y.conv_state[lw.gla_index].p : nullptr;
+            ConvArgs ca{y.proj.p, lw.n_in, lw.conv_off, lw.conv_w, lw.conv_b, cstate, st.row_seq, st.row_pos, st.seq_row0, st.seq_slot, st.seq_pos0,
+                        lw.conv_ch, d.conv, y.cv.p};
+            if (delta)
+                launch(lc, "delta_prep", 0, ly_delta_prep_kernel, dim3(Ti), dim3(256), 0, ca, lw.off_b, lw.off_a, (const float*)lw.dt_bias,
+                       (const float*)lw.a_log, H, G, D, (float)(1.0 / std::sqrt((double)D)), y.rs.p);
+            else
+                launch(lc, "ssm_prep", 0, ly_mamba_prep_kernel, dim3(Ti), dim3(256), 0, ca, lw.off_dt, (const float*)lw.dt_bias, (const float*)lw.a_log, H,
+                       y.rs.p);
+            if (d.conv > 1) launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (lw.conv_ch + 127) / 128), dim3(128), 0, ca);
+            // column offsets inside cv (the convolved span starts at conv_off)
+            RecArgs ra{y.cv.p, lw.conv_ch, lw.off_q - lw.conv_off, lw.off_k - lw.conv_off, lw.off_v - lw.conv_off, y.rs.p,
+                       delta ? (const float*)nullptr : (const float*)lw.dskip, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0, st.seq_slot, st.seq_pos0,
+                       H, G, rows, Dv};
+            if (delta) {
+                launch_rec_scan<true>(lc, ra, n);
+                launch(lc, "gla_out", 0, ly_gla_out_kernel, dim3((Ti * H + 7) / 8), dim3(256), 0, (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g,
+                       (const float*)lw.hnorm, eps, Ti, H, Dv, y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
+            } else {
+                launch_rec_scan<false>(lc, ra, n);
+                const int inner = H * Dv, part = inner / d.norm_groups;
+                launch(lc, "gated_group_norm", 0, ly_gated_group_norm_kernel, dim3(Ti, d.norm_groups), dim3(std::min(1024, std::max(64, (part + 31) / 32 * 32))), 0,
+                       (const float*)y.go.p, (const float*)y.proj.p, lw.n_in, lw.off_g, (const float*)lw.hnorm, eps, inner, d.norm_groups, y.u.p,
+                       lw.tc_o ? uhi : (uint16_t*)nullptr, ulo);
+            }
+        } else if (d.mixer == FL_MIXER_GLA) {
             // decay pre-activation through the rank-r bottleneck: z = W_a2 a (the bias and the sigmoid^(1/tau) are applied by the scan)
             gemm(lc, "gemm_gla_decay", y.proj.p + lw.off_a, lw.n_in, lw.a2, H * D, d.decay_rank, y.la.p, H * D, Ti);
             GlaArgs ga{y.proj.p, lw.n_in, lw.off_q, lw.off_k, lw.off_v, y.la.p, lw.a2b, 1.f / d.tau, y.go.p, y.gla_state[lw.gla_index].p, st.seq_row0,
@@ -700,26 +887,27 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             }
         }
         gemm_tc_or_exact(c, lc, "gemm_mix_out", y.u.p, uhi, ulo, lw.w_o, lw.tm_o, lw.tc_o, W, H * Dv, y.y.p, Ti);
-        const float* next1 = li + 1 < m.L ? m.layers[li + 1].norm1 : nullptr;
-        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm1b,
-               d.ffn != FL_FFN_NONE ? (const float*)lw.norm2 : next1, eps, W, y.h.p, hhi, hlo);
+        const float* next1 = (pre && li + 1 < m.L) ? m.layers[li + 1].norm1 : nullptr;
+        const int more = li + 1 < m.L ? split_x : 0;       // whether another sublayer reads x after this layer
+        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)nullptr, (const float*)lw.norm1b,
+               d.ffn != FL_FFN_NONE ? (const float*)lw.norm2 : next1, eps, W, plain, d.ffn != FL_FFN_NONE ? split_x : more, y.h.p, hhi, hlo);
         if (d.ffn == FL_FFN_NONE) continue;
         const int F = d.ff;
         if (d.ffn == FL_FFN_DENSE) {
-            gemm_tc_or_exact(c, lc, "gemm_ff_in", y.h.p, hhi, hlo, lw.w_gu, lw.tm_gu, lw.tc_gu, 2 * F, W, y.gu.p, Ti);
+            gemm_tc_or_exact(c, lc, "gemm_ff_in", sub_in, hhi, hlo, lw.w_gu, lw.tm_gu, lw.tc_gu, 2 * F, W, y.gu.p, Ti);
             launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                   (const int*)nullptr, Ti, lw.tc_down ? (float*)nullptr : y.act.p, lw.tc_down ? ahi : (uint16_t*)nullptr, alo);
+                   d.ffn_act, (const float*)lw.b_gu, (const int*)nullptr, Ti, lw.tc_down ? (float*)nullptr : y.act.p, lw.tc_down ? ahi : (uint16_t*)nullptr, alo);
             gemm_tc_or_exact(c, lc, "gemm_ff_out", y.act.p, ahi, alo, lw.w_down, lw.tm_down, lw.tc_down, W, F, y.y.p, Ti);
         } else {
             const int E = d.experts, top = d.top, P = Ti * top;
-            launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, (const float*)y.h.p, W, (const float*)lw.router, E, top,
+            launch(lc, "moe_router", 0, ly_router_kernel, dim3(Ti), dim3(256), (size_t)E * 4, sub_in, W, (const float*)lw.router, E, top,
                    (const float*)lw.shared_gate, y.route_sel.p, y.route_w.p, y.sgate.p);
             const float* sh = nullptr;
             if (d.shared_ff > 0) {          // the always-on expert first: its split-K scratch is free again before the routed experts run
                 const int Fs = d.shared_ff;
-                gemm_tc_or_exact(c, lc, "gemm_shared_in", y.h.p, hhi, hlo, lw.s_gu, lw.tm_sgu, lw.tc_sgu, 2 * Fs, W, y.sh_gu.p, Ti);
+                gemm_tc_or_exact(c, lc, "gemm_shared_in", sub_in, hhi, hlo, lw.s_gu, lw.tm_sgu, lw.tc_sgu, 2 * Fs, W, y.sh_gu.p, Ti);
                 launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * Fs + 255) / 256)), dim3(256), 0, (const float*)y.sh_gu.p, Fs,
-                       d.shared_limit, (const int*)nullptr, Ti, lw.tc_sdown ? (float*)nullptr : y.sh_act.p, lw.tc_sdown ? ahi : (uint16_t*)nullptr, alo);
+                       d.shared_limit, 0, (const float*)nullptr, (const int*)nullptr, Ti, lw.tc_sdown ? (float*)nullptr : y.sh_act.p, lw.tc_sdown ? ahi : (uint16_t*)nullptr, alo);
                 gemm_tc_or_exact(c, lc, "gemm_shared_out", y.sh_act.p, ahi, alo, lw.s_down, lw.tm_sdown, lw.tc_sdown, W, Fs, y.sh_o.p, Ti);
                 sh = y.sh_o.p;
             }
@@ -729,7 +917,7 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                 for (int e = 0; e < E; ++e) {
                     dense_gemm(c, lc, "gemm_tc_moe_in", Ti, 2 * F, W, lw.tm_egu[e], y.gu.p, hhi, hlo);
                     launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (Ti * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                           (const int*)nullptr, Ti, (float*)nullptr, ahi, alo);
+                           0, (const float*)nullptr, (const int*)nullptr, Ti, (float*)nullptr, ahi, alo);
                     dense_gemm(c, lc, "gemm_tc_moe_out", Ti, W, F, lw.tm_edown[e], y.eo.p, ahi, alo);
                     launch(lc, "moe_accum", 0, ly_moe_accum_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.route_sel.p,
                            (const float*)y.route_w.p, top, e, (const float*)nullptr, e == 0 ? 1 : 0, W, y.y.p);
@@ -755,10 +943,10 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                            (const int*)y.route_sel.p, (const int*)y.pair_of.p, (const int*)y.grp_off.p, cap, (const float*)y.route_w.p, top, sh,
                            (const float*)y.sgate.p, W, y.y.p);
                 } else {
-                    LyGemm g1{y.h.p, 0, W, y.pair_row.p, lw.w_gu, (long long)2 * F * W, 2 * F, W, y.gu.p, 0, 2 * F, y.grp_off.p, P};
+                    LyGemm g1{sub_in, 0, W, y.pair_row.p, lw.w_gu, (long long)2 * F * W, 2 * F, W, y.gu.p, 0, 2 * F, y.grp_off.p, P};
                     gemm_groups(lc, "gemm_moe_in", g1, E, P);
                     launch(lc, "glu", 0, ly_glu_kernel, dim3(std::min(4 * kNumSMs, (P * F + 255) / 256)), dim3(256), 0, (const float*)y.gu.p, F, d.limit,
-                           (const int*)nullptr, P, y.act.p, (uint16_t*)nullptr, (uint16_t*)nullptr);
+                           0, (const float*)nullptr, (const int*)nullptr, P, y.act.p, (uint16_t*)nullptr, (uint16_t*)nullptr);
                     LyGemm g2{y.act.p, 0, F, nullptr, lw.w_down, (long long)W * F, W, F, y.eo.p, 0, W, y.grp_off.p, P};
                     gemm_groups(lc, "gemm_moe_out", g2, E, P);
                     launch(lc, "moe_combine", 0, ly_moe_combine_kernel, gw, dim3(256), 0, (const float*)y.eo.p, (const int*)y.pair_of.p,
@@ -766,11 +954,11 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                 }
             }
         }
-        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.norm2b, next1, eps, W, y.h.p,
-               hhi, hlo);
+        launch(lc, "post_norm", 0, ly_post_norm_kernel, dim3(Ti), dim3(nthr), 0, y.x.p, (const float*)y.y.p, (const float*)lw.b_down, (const float*)lw.norm2b,
+               next1, eps, W, plain, more, y.h.p, hhi, hlo);
     }
     if (n_want > 0) {
-        launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, y.hf.p,
+        launch(lc, "final_norm", 0, ly_final_norm_kernel, dim3(n_want), dim3(nthr), 0, (const float*)y.x.p, st.want, (const float*)m.final_norm, eps, W, plain, y.hf.p,
                m.tc_head ? y.hf_hi.p : (uint16_t*)nullptr, y.hf_lo.p);
         gemm_tc_or_exact(c, lc, "gemm_head", y.hf.p, m.tc_head ? y.hf_hi.p : nullptr, y.hf_lo.p, m.head, m.tm_head, m.tc_head, m.V, W, y.logits.p, n_want);
     }

@@ -1,6 +1,7 @@
-// Layered decoder (FL_ARCH_NIFUNEX): model / cache objects shared by fl_layered.cu and fl_lib.cu.
-// A layer = one mixer (gated linear attention | latent attention) + an optional feed-forward (dense | MoE with shared expert),
-// each wrapped by a norm before and after.  Sizes and constants come from fl_layer_desc; nothing is fixed per model.
+// Layered decoders (FL_ARCH_NIFUNEX, FL_ARCH_ROFETAR): model / cache objects shared by fl_layered.cu and fl_lib.cu.
+// A layer = one mixer (gated linear attention | latent attention | grouped-query attention | Mamba-2 | gated delta rule) + an
+// optional feed-forward (dense | MoE with shared expert), each wrapped by a norm before and after, or after only
+// (fl_stack_config.no_pre_norm).  Sizes and constants come from fl_layer_desc; nothing is fixed per model.
 #pragma once
 #include <cuda.h>
 
@@ -21,9 +22,17 @@ struct LayeredLayerW {
     float *norm1 = nullptr, *norm1b = nullptr, *norm2 = nullptr, *norm2b = nullptr;     // [W] f32
     // mixer input projections stacked into ONE matrix [n_in, W] (one GEMM per layer):
     //   GLA:     q | k | v | g | a1        latent attention:  q | dkv   (no dkv rows when kv_from >= 0)
+    //   attention:  q | k | v  (no k, v rows when kv_from >= 0)      Mamba-2:  z | x | B | C | dt      delta rule:  q | k | v | g | b | a
+    // (rows padded with zeros to a multiple of 8 for the three newer mixers, so that the tensor-core GEMM's tiles fit)
     uint16_t* w_in = nullptr;
     int n_in = 0;
     int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_a = 0, off_dkv = 0;             // row (= output column) offsets inside w_in
+    int off_b = 0, off_dt = 0;          // delta rule: write strengths; Mamba-2: step sizes
+    int conv_off = 0, conv_ch = 0;      // recurrent mixers with a short convolution: the convolved columns of w_in's output
+    float *conv_w = nullptr, *conv_b = nullptr;                                         // [conv_ch, taps], [conv_ch] (zeros when the design has none)
+    float *a_log = nullptr, *dt_bias = nullptr, *dskip = nullptr;                       // [heads]
+    float *qnorm = nullptr, *knorm = nullptr;                                           // attention: [dim]
+    float *b_gu = nullptr, *b_down = nullptr;                                           // biased dense feed-forward: [2 ff], [W]
     uint16_t* w_o = nullptr;            // [W, heads * vdim]
     // GLA
     uint16_t* a2 = nullptr;             // [heads*dim, rank]
@@ -35,7 +44,7 @@ struct LayeredLayerW {
     int kv_owner = -1;                  // layer whose cache this layer reads (itself when it projects its own)
     int kv_index = -1;                  // index of that cache among the model's latent caches
     int rope_index = -1;                // index into the model's distinct rotary tables
-    int gla_index = -1;                 // index among the model's recurrent layers
+    int gla_index = -1;                 // index among the model's recurrent layers (GLA, Mamba-2, delta rule)
     // feed-forward: groups 0..E-1 = experts (or the one dense block), `shared` separate
     uint16_t *w_gu = nullptr, *w_down = nullptr;        // [groups][2 ff, W] (gate rows then up rows), [groups][W, ff]
     uint16_t *s_gu = nullptr, *s_down = nullptr;        // shared expert
@@ -63,7 +72,7 @@ struct LayeredModel {
     bool f32 = false;                   // compute_dtype == FL_DTYPE_F32
     std::vector<LayeredLayerW> layers;
     std::vector<RopeSpec> ropes;
-    std::vector<int> kv_layers, gla_layers;            // layers that own a latent cache / a recurrent state
+    std::vector<int> kv_layers, gla_layers;            // layers that own a paged cache (latent, or keys | values) / a recurrent state
     DevBuf<uint8_t> slab;
     uint16_t *embed = nullptr, *head = nullptr;
     float* final_norm = nullptr;
@@ -75,7 +84,7 @@ struct LayeredModel {
     bool finalized = false;
     uint64_t weight_bytes = 0;
     // widest sizes over the layers (workspace planning)
-    int max_in = 0, max_hv = 0, max_hd = 0, max_hc = 0, max_ff = 0, max_top = 0, max_experts = 0;
+    int max_in = 0, max_hv = 0, max_hd = 0, max_hc = 0, max_ff = 0, max_top = 0, max_experts = 0, max_cv = 0, max_heads = 0;
     std::mutex mu;
 };
 
@@ -83,9 +92,10 @@ struct LayeredModel {
 struct LayeredCache {
     PagePool pool;
     bool f32 = false;
-    std::vector<void*> kv_pool;         // per latent cache: [pages][64][kv_rank + rot_dim] (float or bf16)
+    std::vector<void*> kv_pool;         // per paged cache: [pages][64][kv_rank + rot_dim] or [pages][64][kv_heads * (dim + vdim)] (float or bf16)
     std::vector<DevBuf<uint8_t>> kv_store;
-    std::vector<DevBuf<float>> gla_state;          // per recurrent layer: [slots][heads][dim][vdim]
+    std::vector<DevBuf<float>> gla_state;          // per recurrent layer: [slots][heads][dim | state][vdim]
+    std::vector<DevBuf<float>> conv_state;         // per recurrent layer: [slots][taps - 1][conv_ch] (empty without a convolution)
     std::vector<DevBuf<float>> rope_cos, rope_sin; // per RopeSpec: [max_seq][dims/2]
     DevBuf<int> page_table;             // [slots][pages_per_slot]
     DevBuf<int> step_tab;               // per-step integer tables (see StepTab in fl_layered.cu)
@@ -94,6 +104,7 @@ struct LayeredCache {
     // workspace for `rows` tokens of a step
     size_t rows = 0, want_cap = 0;
     DevBuf<float> x, h, y, proj, la, u, go, qa, ol, gu, act, eo, sh_gu, sh_act, sh_o, route_w, sgate, hf, logits;
+    DevBuf<float> cv, rs;               // recurrent mixers: convolved + activated columns [rows, max_cv]; per-head (decay, strength) [rows, 2 heads]
     DevBuf<int> route_sel, pair_row, pair_of, grp_off;
     PinnedBuf<float> h_logits;
     // serving precision: hi/lo halves of the activations that feed tensor-core GEMMs, and the split-K slices of their outputs

@@ -1,6 +1,8 @@
-// Kernels of the layered decoder (sm_100a): residual / norm glue, the exact-f32 GEMM, gated linear attention (decay, scan, head
-// norm + gate), latent attention over the paged latent cache (append + rotary, absorbed-query attention), the clamped GLU
-// feed-forward and the mixture-of-experts router / row lists / combine.  Every mechanism takes its sizes and constants as
+// Kernels of the layered decoders (sm_100a): residual / norm glue, the exact-f32 GEMM, gated linear attention (decay, scan, head
+// norm + gate), latent attention over the paged latent cache (append + rotary, absorbed-query attention), grouped-query attention
+// with per-head q/k norm, score cap and softmax sink, the short-convolution recurrent mixers (Mamba-2, gated delta rule: prep, scan,
+// gated norms), the GLU feed-forward (clamped swish or tanh-gelu, optional biases) and the mixture-of-experts router / row lists /
+// combine.  Every mechanism takes its sizes and constants as
 // arguments.  Residual stream, norms, softmax, routers, decays and the recurrent state are f32 throughout; a row's result never
 // depends on which other rows share the launch (fixed summation order per output element).
 #pragma once
@@ -66,9 +68,14 @@ static __global__ void ly_sum_slices_kernel(const float* __restrict__ y, int nsl
 }
 
 // ---- embedding + first norm ------------------------------------------------------------------------------------------------
-// x[row] = embed[tok[row]];  h[row] = x / sqrt(mean x^2 + eps) * (1 + w)
+// A norm weight w scales by (1 + w), or by w itself when `plain`.
+__device__ __forceinline__ float norm_scale(const float* __restrict__ w, int c, int plain) { return plain ? w[c] : 1.f + w[c]; }
+
+// x[row] = embed[tok[row]];  h[row] = x / sqrt(mean x^2 + eps) * scale(w).  nw == nullptr (the first sublayer reads the stream
+// itself): h is not written and the hi | lo halves are those of x.
 static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, const int* __restrict__ tok, int W, const float* __restrict__ nw,
-                                            float eps, float* __restrict__ x, float* __restrict__ h, uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
+                                            float eps, int plain, float* __restrict__ x, float* __restrict__ h, uint16_t* __restrict__ hhi,
+                                            uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const int row = blockIdx.x;
     const uint16_t* e = embed + (size_t)tok[row] * W;
@@ -78,38 +85,45 @@ static __global__ void ly_embed_norm_kernel(const uint16_t* __restrict__ embed, 
         const float v = __uint_as_float((uint32_t)e[c] << 16);
         xr[c] = v;
         ss += v * v;
+        if (nw == nullptr) split_store(hhi, hlo, (size_t)row * W + c, v);
     }
+    if (nw == nullptr) return;
     const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
     float* hr = h + (size_t)row * W;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = xr[c] * r * (1.f + nw[c]);
+        const float v = xr[c] * r * norm_scale(nw, c, plain);
         hr[c] = v;
         split_store(hhi, hlo, (size_t)row * W + c, v);
     }
 }
 
-// x[row] += norm(y[row]; wb);  then, if wnext, h[row] = norm(x[row]; wnext)      (norm: zero-centred weight: the scale is 1 + w)
-static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ wb,
-                                           const float* __restrict__ wnext, float eps, int W, float* __restrict__ h, uint16_t* __restrict__ hhi,
-                                           uint16_t* __restrict__ hlo) {
+// x[row] += norm(y[row] + yb; wb);  then, if wnext, h[row] = norm(x[row]; wnext); else, if split_x, the hi | lo halves of x[row]
+// itself (the next sublayer reads the stream un-normed).  yb: optional bias of the projection that produced y.
+static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* __restrict__ y, const float* __restrict__ yb, const float* __restrict__ wb,
+                                           const float* __restrict__ wnext, float eps, int W, int plain, int split_x, float* __restrict__ h,
+                                           uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const int row = blockIdx.x;
     const float* yr = y + (size_t)row * W;
     float* xr = x + (size_t)row * W;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < W; c += blockDim.x) ss += yr[c] * yr[c];
+    for (int c = threadIdx.x; c < W; c += blockDim.x) {
+        const float v = yr[c] + (yb ? yb[c] : 0.f);
+        ss += v * v;
+    }
     const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
     float s2 = 0.f;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = xr[c] + yr[c] * r * (1.f + wb[c]);
+        const float v = xr[c] + (yr[c] + (yb ? yb[c] : 0.f)) * r * norm_scale(wb, c, plain);
         xr[c] = v;
         s2 += v * v;
+        if (wnext == nullptr && split_x) split_store(hhi, hlo, (size_t)row * W + c, v);
     }
     if (wnext == nullptr) return;
     const float r2 = 1.f / sqrtf(block_sum(s2, red) / (float)W + eps);
     float* hr = h + (size_t)row * W;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = xr[c] * r2 * (1.f + wnext[c]);
+        const float v = xr[c] * r2 * norm_scale(wnext, c, plain);
         hr[c] = v;
         split_store(hhi, hlo, (size_t)row * W + c, v);
     }
@@ -117,7 +131,7 @@ static __global__ void ly_post_norm_kernel(float* __restrict__ x, const float* _
 
 // hf[i] = norm(x[want[i]]; w): the rows that go on to the vocabulary projection
 static __global__ void ly_final_norm_kernel(const float* __restrict__ x, const int* __restrict__ want, const float* __restrict__ w, float eps, int W,
-                                            float* __restrict__ hf, uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
+                                            int plain, float* __restrict__ hf, uint16_t* __restrict__ hhi, uint16_t* __restrict__ hlo) {
     __shared__ float red[33];
     const float* xr = x + (size_t)want[blockIdx.x] * W;
     float ss = 0.f;
@@ -125,7 +139,7 @@ static __global__ void ly_final_norm_kernel(const float* __restrict__ x, const i
     const float r = 1.f / sqrtf(block_sum(ss, red) / (float)W + eps);
     float* hr = hf + (size_t)blockIdx.x * W;
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-        const float v = xr[c] * r * (1.f + w[c]);
+        const float v = xr[c] * r * norm_scale(w, c, plain);
         hr[c] = v;
         split_store(hhi, hlo, (size_t)blockIdx.x * W + c, v);
     }
@@ -541,17 +555,373 @@ static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const
     }
 }
 
+// ---- grouped-query attention over a paged key | value cache ---------------------------------------------------------------------
+// Cache row of a token: [kv_heads][dim] keys (normed, rotated) then [kv_heads][vdim] values.
+struct AttnPrepArgs {
+    float* proj; int ldp, off_q, off_k, off_v;  // off_k < 0: the layer reads another layer's cache (queries are still prepared)
+    const float *qnorm, *knorm; float eps;       // [dim] each
+    void* pool; const int* page_table; int pps;
+    const int *row_seq, *row_pos, *seq_slot;
+    const float *cosb, *sinb;                    // [max_seq][rdims / 2], already multiplied by the YaRN magnitude
+    int H, G, D, Dv, rdims, halves;
+};
+// Per row: every query head and (when the layer owns its cache) every key head is RMS-normed over dim with a weight shared by the
+// heads, then its first rdims channels are turned by the row's position: pairs (i, i + rdims/2) when `halves`, else (2i, 2i+1).
+// Queries are rewritten in place, keys and values go to the row's cache page.  One warp per head in turn.
+template <typename CT>
+static __global__ void __launch_bounds__(128) ly_attn_prep_kernel(AttnPrepArgs a) {
+    extern __shared__ float sm[];               // [4 warps][D]
+    const int row = blockIdx.x, pos = a.row_pos[row], lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    float* pr = a.proj + (size_t)row * a.ldp;
+    const int half = a.rdims / 2;
+    const float* cs = a.cosb + (size_t)pos * half;
+    const float* sn = a.sinb + (size_t)pos * half;
+    float* buf = sm + wid * a.D;
+    const bool own = a.off_k >= 0;
+    CT* dst = nullptr;
+    if (own) {
+        const int slot = a.seq_slot[a.row_seq[row]];
+        const int page = a.page_table[(size_t)slot * a.pps + pos / kKvPage];
+        dst = (CT*)a.pool + ((size_t)page * kKvPage + pos % kKvPage) * ((size_t)a.G * (a.D + a.Dv));
+    }
+    const int items = a.H + (own ? a.G : 0);
+    for (int it = wid; it < items; it += 4) {
+        const bool isq = it < a.H;
+        float* src = isq ? pr + a.off_q + it * a.D : pr + a.off_k + (it - a.H) * a.D;
+        const float* w = isq ? a.qnorm : a.knorm;
+        float ss = 0.f;
+        for (int c = lane; c < a.D; c += 32) ss += src[c] * src[c];
+        const float r = 1.f / sqrtf(warp_sum(ss) / (float)a.D + a.eps);
+        for (int c = lane; c < a.D; c += 32) buf[c] = src[c] * r * w[c];
+        __syncwarp();
+        for (int c = lane; c < a.D; c += 32) {
+            float val = buf[c];
+            if (c < a.rdims) {
+                int pi, second;
+                if (a.halves) { second = c >= half; pi = second ? c - half : c; }
+                else { second = c & 1; pi = c >> 1; }
+                const int cu = a.halves ? pi : 2 * pi, cv = a.halves ? pi + half : 2 * pi + 1;
+                const float u = buf[cu], v = buf[cv];
+                val = second ? v * cs[pi] + u * sn[pi] : u * cs[pi] - v * sn[pi];
+            }
+            if (isq) src[c] = val; else st_c(dst + (size_t)(it - a.H) * a.D + c, val);
+        }
+        __syncwarp();
+    }
+    if (own) {
+        const float* v = pr + a.off_v;
+        CT* vd = dst + (size_t)a.G * a.D;
+        for (int c = threadIdx.x; c < a.G * a.Dv; c += blockDim.x) st_c(vd + c, v[c]);
+    }
+}
+
+struct GqaAttnArgs {
+    const float* proj; int ldp, off_q;          // prepared queries at proj[row, off_q + h * D ...]
+    const void* pool; const int* page_table; int pps;
+    const int *row_seq, *row_pos, *seq_slot;
+    float* out;                 // [T, H * Dv]
+    uint16_t *ohi, *olo;        // its hi | lo halves (nullptr: not wanted)
+    int H, G, D, Dv, window;
+    float scale, softcap;       // softcap 0 = scores are used as they are
+    int sink;                   // 1: the denominator gets exp(0) more
+    int row_base;
+};
+constexpr int kGqaWarps = 8;
+// One block per (row, head).  score_j = cap(q . k_j * scale) over the keys j <= pos (and inside the window, if any), softmax in
+// f32 with the optional sink, out = sum_j p_j v_j.  Warp w of the eight folds keys j0 + w, j0 + w + 8, ... into an online softmax
+// (lanes own CPL consecutive channels of the key and of the value); the partial results are merged in warp order.  Which warp
+// takes which key depends on the position alone.
+template <typename CT, int CPL>
+static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaAttnArgs a) {
+    extern __shared__ float sm[];               // [warps][Dv] accumulators, then [warps][2] (max, sum)
+    const int row = a.row_base + blockIdx.x, hd = blockIdx.y, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int D = a.D, Dv = a.Dv, g = hd / (a.H / a.G);
+    const size_t E = (size_t)a.G * (D + Dv);
+    const int pos = a.row_pos[row], slot = a.seq_slot[a.row_seq[row]];
+    const int j0 = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    float q[CPL], acc[CPL];
+    const float* qp = a.proj + (size_t)row * a.ldp + a.off_q + hd * D;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; q[i] = c < D ? qp[c] * a.scale : 0.f; acc[i] = 0.f; }
+    float m = -INFINITY, l = 0.f;
+    const int* pt = a.page_table + (size_t)slot * a.pps;
+    const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+    constexpr int KU = 2;
+    for (int j = j0 + wid; j <= pos; j += kGqaWarps * KU) {
+        float val[KU][CPL], dot[KU];
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            const int jj = j + u * kGqaWarps;
+            dot[u] = 0.f;
+            if (jj <= pos) {
+                const CT* kp = (const CT*)a.pool + ((size_t)pt[jj / kKvPage] * kKvPage + jj % kKvPage) * E;
+                float kk[CPL];
+                load_chunk<CPL>(kp + (size_t)g * D, lane * CPL, D, kk);
+                load_chunk<CPL>(kp + (size_t)a.G * D + (size_t)g * Dv, lane * CPL, Dv, val[u]);
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) dot[u] = fmaf(q[i], kk[i], dot[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) val[u][i] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < KU; ++u) dot[u] = warp_sum(dot[u]);
+#pragma unroll
+        for (int u = 0; u < KU; ++u) {
+            if (j + u * kGqaWarps > pos) break;
+            float sc = dot[u];
+            if (a.softcap > 0.f) sc = a.softcap * tanhf(sc * inv_cap);
+            const float mn = fmaxf(m, sc), corr = expf(m - mn), p = expf(sc - mn);
+            l = l * corr + p;
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) acc[i] = acc[i] * corr + p * val[u][i];
+            m = mn;
+        }
+    }
+    float* sacc = sm;
+    float* sml = sm + kGqaWarps * Dv;
+#pragma unroll
+    for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; if (c < Dv) sacc[wid * Dv + c] = acc[i]; }
+    if (lane == 0) { sml[2 * wid] = m; sml[2 * wid + 1] = l; }
+    __syncthreads();
+    float M = a.sink ? 0.f : -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kGqaWarps; ++w) M = fmaxf(M, sml[2 * w]);
+    float f[kGqaWarps], Lsum = a.sink ? expf(-M) : 0.f;
+#pragma unroll
+    for (int w = 0; w < kGqaWarps; ++w) { f[w] = expf(sml[2 * w] - M); Lsum += sml[2 * w + 1] * f[w]; }
+    const float inv = 1.f / Lsum;
+    const size_t ob = ((size_t)row * a.H + hd) * Dv;
+    for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < kGqaWarps; ++w) t += sacc[w * Dv + c] * f[w];
+        t *= inv;
+        a.out[ob + c] = t;
+        split_store(a.ohi, a.olo, ob + c, t);
+    }
+}
+
+// ---- recurrent mixers with a short causal convolution (Mamba-2, gated delta rule) --------------------------------------------------
+__device__ __forceinline__ float softplusf_(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float siluf_(float z) { return z * sigmoidf_(z); }
+
+constexpr int kMaxTaps = 16;
+struct ConvArgs {
+    const float* proj; int ldp, off;            // the convolved columns are proj[row, off .. off + ch)
+    const float *w, *b;                         // [ch, taps], [ch] or nullptr
+    float* state;                               // [slots][taps - 1][ch]: the inputs of the taps - 1 positions before the step, oldest first
+    const int *row_seq, *row_pos, *seq_row0, *seq_slot, *seq_pos0;
+    int ch, taps;
+    float* cv;                                  // [T, ch]: silu(conv)
+};
+// Input of channel c at position p - back of the row's sequence: a row of this step, the slot's carried inputs, or zero before the start.
+__device__ __forceinline__ float conv_input(const ConvArgs& a, int row, int row0, int pos, int pos0, int slot, int back, int c) {
+    if (row - back >= row0) return a.proj[(size_t)(row - back) * a.ldp + a.off + c];
+    const int p = pos - back;
+    if (p < 0) return 0.f;
+    return a.state[((size_t)slot * (a.taps - 1) + (p - pos0 + a.taps - 1)) * a.ch + c];
+}
+__device__ __forceinline__ float conv_silu(const ConvArgs& a, int row, int row0, int pos, int pos0, int slot, int c) {
+    float t = a.b ? a.b[c] : 0.f;
+    for (int k = 0; k < a.taps; ++k) t = fmaf(a.w[(size_t)c * a.taps + k], conv_input(a, row, row0, pos, pos0, slot, a.taps - 1 - k, c), t);
+    return siluf_(t);
+}
+// After the rows of a step were convolved: the slot keeps the last taps - 1 inputs of each sequence.  grid (sequences, channel blocks).
+static __global__ void ly_conv_state_kernel(ConvArgs a) {
+    const int seq = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= a.ch) return;
+    const int r0 = a.seq_row0[seq], n = a.seq_row0[seq + 1] - r0, pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
+    float keep[kMaxTaps];
+    const int last_row = r0 + n - 1, last_pos = pos0 + n - 1;
+    for (int i = 0; i < a.taps - 1; ++i) keep[i] = conv_input(a, last_row, r0, last_pos, pos0, slot, a.taps - 2 - i, c);
+    for (int i = 0; i < a.taps - 1; ++i) a.state[((size_t)slot * (a.taps - 1) + i) * a.ch + c] = keep[i];
+}
+
+// Mamba-2, per row: x | B | C <- silu(conv + bias);  per head  b = softplus(dt + dt_bias),  a = exp(-exp(A_log) b)  -> ab[row, h] = (a, b)
+static __global__ void ly_mamba_prep_kernel(ConvArgs a, int off_dt, const float* __restrict__ dt_bias, const float* __restrict__ a_log, int H,
+                                            float* __restrict__ ab) {
+    const int row = blockIdx.x, seq = a.row_seq[row], pos = a.row_pos[row];
+    const int row0 = a.seq_row0[seq], pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
+    for (int c = threadIdx.x; c < a.ch; c += blockDim.x) a.cv[(size_t)row * a.ch + c] = conv_silu(a, row, row0, pos, pos0, slot, c);
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float dt = softplusf_(a.proj[(size_t)row * a.ldp + off_dt + h] + dt_bias[h]);
+        ab[((size_t)row * H + h) * 2] = expf(-expf(a_log[h]) * dt);
+        ab[((size_t)row * H + h) * 2 + 1] = dt;
+    }
+}
+
+// Gated delta rule, per row: q | k | v <- silu(conv);  q, k heads -> unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times qscale;
+// per head  b = sigmoid(proj[off_b + h]),  a = exp(-exp(A_log) softplus(proj[off_a + h] + dt_bias))  -> ab[row, h] = (a, b)
+static __global__ void ly_delta_prep_kernel(ConvArgs a, int off_b, int off_a, const float* __restrict__ dt_bias, const float* __restrict__ a_log, int H,
+                                            int G, int D, float qscale, float* __restrict__ ab) {
+    const int row = blockIdx.x, seq = a.row_seq[row], pos = a.row_pos[row];
+    const int row0 = a.seq_row0[seq], pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
+    float* cvr = a.cv + (size_t)row * a.ch;
+    for (int c = threadIdx.x; c < a.ch; c += blockDim.x) cvr[c] = conv_silu(a, row, row0, pos, pos0, slot, c);
+    for (int h = threadIdx.x; h < H; h += blockDim.x) {
+        const float* pr = a.proj + (size_t)row * a.ldp;
+        ab[((size_t)row * H + h) * 2] = expf(-expf(a_log[h]) * softplusf_(pr[off_a + h] + dt_bias[h]));
+        ab[((size_t)row * H + h) * 2 + 1] = sigmoidf_(pr[off_b + h]);
+    }
+    __syncthreads();
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int it = wid; it < 2 * G; it += nw) {          // q heads, then k heads
+        float* v = cvr + (size_t)it * D;
+        float ss = 0.f;
+        for (int c = lane; c < D; c += 32) ss += v[c] * v[c];
+        const float r = (it < G ? qscale : 1.f) / sqrtf(warp_sum(ss) + 1e-6f);
+        for (int c = lane; c < D; c += 32) v[c] *= r;
+    }
+}
+
+struct RecArgs {
+    const float* cv; int ldc, off_q, off_k, off_v;      // read-out vector q[g], write vector k[g] (D channels each), value v[h] (Dv channels)
+    const float* ab;            // [T, H, 2]: decay a, strength b
+    const float* dskip;         // [H] or nullptr: o += dskip[h] * v
+    float* o;                   // [T, H * Dv]
+    float* state;               // [slots][H][D][Dv]
+    const int *seq_row0, *seq_slot, *seq_pos0;
+    int H, G, D, Dv;
+};
+// Token by token, per head:  S <- a S;  u = b v   (DELTA: u = b (v - S^T k));  S <- S + k u^T;  o = S^T q (+ dskip v).
+// One block per (sequence, head, 32 value columns) -- columns of S never interact; thread (vcol, dg) keeps rows dg, dg + 8, ... of its
+// column in registers.  The next token's operands travel into registers while the current one is folded.  The order of operations per
+// token does not depend on how a prompt was cut.
+template <int RPT, bool DELTA>
+static __global__ void __launch_bounds__(kGlaVS * kGlaDG) ly_rec_scan_kernel(RecArgs a) {
+    extern __shared__ float sm[];
+    const int D = a.D, Dv = a.Dv;
+    float* sq = sm;                     // [2][D]
+    float* sk = sq + 2 * D;             // [2][D]
+    float* sv = sk + 2 * D;             // [2][32]
+    float* sab = sv + 2 * kGlaVS;       // [2][2]
+    float* red = sab + 4;               // [2][8][32] read-out partials
+    float* red1 = red + 2 * kGlaDG * kGlaVS;    // [8][32] S^T k partials (DELTA)
+    const int seq = blockIdx.x, hd = blockIdx.y, v0 = blockIdx.z * kGlaVS, g = hd / (a.H / a.G);
+    const int tid = threadIdx.x, vc = tid & 31, dg = tid >> 5;
+    const int r0 = a.seq_row0[seq], r1 = a.seq_row0[seq + 1];
+    const bool vok = v0 + vc < Dv;
+    float* st = a.state + (((size_t)a.seq_slot[seq] * a.H + hd) * D) * Dv + v0 + vc;
+    float s[RPT];
+    const bool fresh = a.seq_pos0[seq] == 0;
+#pragma unroll
+    for (int i = 0; i < RPT; ++i) {
+        const int d = dg + kGlaDG * i;
+        s[i] = (!fresh && vok && d < D) ? st[(size_t)d * Dv] : 0.f;
+    }
+    const bool ld_d = tid < D, ld_v = tid < kGlaVS, ld_s = tid >= 32 && tid < 34;
+    const float dsk = a.dskip ? a.dskip[hd] : 0.f;
+    float rq = 0.f, rk = 0.f, rv = 0.f, rs = 0.f;
+    auto fetch = [&](int row) {
+        const float* pr = a.cv + (size_t)row * a.ldc;
+        if (ld_d) { rq = pr[a.off_q + g * D + tid]; rk = pr[a.off_k + g * D + tid]; }
+        if (ld_v) rv = (v0 + tid < Dv) ? pr[a.off_v + hd * Dv + v0 + tid] : 0.f;
+        if (ld_s) rs = a.ab[((size_t)row * a.H + hd) * 2 + (tid - 32)];
+    };
+    auto stage = [&](int b) {
+        if (ld_d) { sq[b * D + tid] = rq; sk[b * D + tid] = rk; }
+        if (ld_v) sv[b * kGlaVS + tid] = rv;
+        if (ld_s) sab[b * 2 + (tid - 32)] = rs;
+    };
+    auto finish = [&](int row, int b) {
+        if (dg == 0 && vok) {
+            const float* rp = red + b * kGlaDG * kGlaVS;
+            float t = 0.f;
+#pragma unroll
+            for (int k = 0; k < kGlaDG; ++k) t += rp[k * kGlaVS + vc];
+            a.o[(size_t)row * a.H * Dv + hd * Dv + v0 + vc] = t + dsk * sv[b * kGlaVS + vc];
+        }
+    };
+    if (r0 < r1) { fetch(r0); stage(0); }
+    int b = 0;
+    for (int row = r0; row < r1; ++row, b ^= 1) {
+        if (row + 1 < r1) fetch(row + 1);
+        __syncthreads();
+        if (row > r0) finish(row - 1, b ^ 1);
+        const float v = sv[b * kGlaVS + vc], da = sab[b * 2], db = sab[b * 2 + 1];
+        float u;
+        if (DELTA) {
+            float part = 0.f;
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) {
+                const int d = dg + kGlaDG * i;
+                if (d < D) { s[i] *= da; part = fmaf(s[i], sk[b * D + d], part); }
+            }
+            red1[dg * kGlaVS + vc] = part;
+            __syncthreads();
+            float r = 0.f;
+#pragma unroll
+            for (int k = 0; k < kGlaDG; ++k) r += red1[k * kGlaVS + vc];
+            u = db * (v - r);
+        } else {
+#pragma unroll
+            for (int i = 0; i < RPT; ++i) s[i] *= da;
+            u = db * v;
+        }
+        float acc = 0.f;
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            const int d = dg + kGlaDG * i;
+            if (d < D) {
+                s[i] = fmaf(sk[b * D + d], u, s[i]);
+                acc = fmaf(s[i], sq[b * D + d], acc);
+            }
+        }
+        red[(b * kGlaDG + dg) * kGlaVS + vc] = acc;
+        if (row + 1 < r1) stage(b ^ 1);
+    }
+    __syncthreads();
+    if (r0 < r1) finish(r1 - 1, b ^ 1);
+    if (vok) {
+#pragma unroll
+        for (int i = 0; i < RPT; ++i) {
+            const int d = dg + kGlaDG * i;
+            if (d < D) st[(size_t)d * Dv] = s[i];
+        }
+    }
+}
+
+// u[row, part] = v / sqrt(mean_part v^2 + eps) * w,  v = y * silu(z): the gated output of Mamba-2, normed in `parts` equal pieces of
+// the inner width.  z = proj[row, off_z ...].  One block per (row, part).
+static __global__ void ly_gated_group_norm_kernel(const float* __restrict__ y, const float* __restrict__ proj, int ldp, int off_z,
+                                                  const float* __restrict__ w, float eps, int inner, int parts, float* __restrict__ u,
+                                                  uint16_t* __restrict__ uhi, uint16_t* __restrict__ ulo) {
+    __shared__ float red[33];
+    const int row = blockIdx.x, n = inner / parts, c0 = blockIdx.y * n;
+    const float* yr = y + (size_t)row * inner + c0;
+    const float* zr = proj + (size_t)row * ldp + off_z + c0;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = yr[c] * siluf_(zr[c]); ss += v * v; }
+    const float r = 1.f / sqrtf(block_sum(ss, red) / (float)n + eps);
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const float v = yr[c] * siluf_(zr[c]) * r * w[c0 + c];
+        u[(size_t)row * inner + c0 + c] = v;
+        split_store(uhi, ulo, (size_t)row * inner + c0 + c, v);
+    }
+}
+
 // ---- feed-forward ----------------------------------------------------------------------------------------------------------
-// act[p, f] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[p, f], limit),  u = clamp(gu[p, F + f], -limit, limit);  p < *count
-static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float limit, const int* __restrict__ count, int rows, float* __restrict__ act,
-                                     uint16_t* __restrict__ ahi, uint16_t* __restrict__ alo) {
+// act 0: act[p, f] = g * sigmoid(1.702 g) * (u + 1),  g = min(gu[p, f], limit),  u = clamp(gu[p, F + f], -limit, limit);
+// act 1: act[p, f] = gelu_tanh(g) * u,  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).  bias [2F] (optional) is added
+// to gate | up first.  p < *count
+__device__ __forceinline__ float glu_value(float g, float u, int act, float limit) {
+    if (act == 1) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g * sigmoidf_(1.702f * g) * (u + 1.f);
+}
+static __global__ void ly_glu_kernel(const float* __restrict__ gu, int F, float limit, int act_kind, const float* __restrict__ bias,
+                                     const int* __restrict__ count, int rows, float* __restrict__ act, uint16_t* __restrict__ ahi,
+                                     uint16_t* __restrict__ alo) {
     const int n = count ? *count : rows;
     const size_t total = (size_t)n * F;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t p = i / F, f = i - p * F;
-        const float g = fminf(gu[p * 2 * F + f], limit);
-        const float u = fminf(fmaxf(gu[p * 2 * F + F + f], -limit), limit);
-        const float v = g * sigmoidf_(1.702f * g) * (u + 1.f);
+        const float g = gu[p * 2 * F + f] + (bias ? bias[f] : 0.f);
+        const float u = gu[p * 2 * F + F + f] + (bias ? bias[F + f] : 0.f);
+        const float v = glu_value(g, u, act_kind, limit);
         if (act != nullptr) act[i] = v;         // nullptr: only the hi | lo halves are consumed (a tensor-core GEMM follows)
         split_store(ahi, alo, i, v);
     }

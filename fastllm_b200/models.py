@@ -475,7 +475,7 @@ class MixtralWithConfig(MistralWithConfig):
 
 
 class NifunexCache(_OffsetCache):
-    """Cache handle of the layered decoder: owns the device cache (latent pages + recurrent-state slots), created on first use."""
+    """Cache handle of the layered decoders: owns the device cache (latent pages + recurrent-state slots), created on first use."""
 
     def __init__(self):
         super().__init__()
@@ -489,7 +489,7 @@ def nifunex_layer_descs(config: dict, decay_ranks: dict):
     arr = (_lib.FlLayerDesc * len(layers))()
     for i, l in enumerate(layers):
         d, m = arr[i], l["mixer"]
-        if l["type"] not in _lib.FL_MIXER:
+        if l["type"] not in ("gla", "latent_attention"):
             raise FastllmError(-1, f"layer {i}: unknown mixer type {l['type']!r}")
         d.mixer = _lib.FL_MIXER[l["type"]]
         d.heads, d.dim, d.vdim = int(m["heads"]), int(m["dim"]), int(m["vdim"])
@@ -503,72 +503,81 @@ def nifunex_layer_descs(config: dict, decay_ranks: dict):
             d.rot_dim, d.kv_rank = int(m["rot_dim"]), int(m["kv_rank"])
             d.kv_from = int(m["kv_from"]) if m.get("kv_from") is not None else -1
             d.window = int((m.get("mask") or {}).get("size") or 0)
-            rot = m.get("rot") or {}
-            d.rot_dims = int(rot.get("dims", d.rot_dim))
-            d.rot_base = float(rot.get("base", 10000.0))
             d.scale = float(m["scale"])
-            sc = rot.get("scaling")
-            if sc:
-                d.yarn_factor, d.yarn_original = float(sc["factor"]), float(sc["original"])
-                d.yarn_fast, d.yarn_slow = float(sc["fast"]), float(sc["slow"])
-        mlp = l.get("mlp")
-        if not mlp:
-            d.ffn = _lib.FL_FFN["none"]
-        elif mlp["kind"] == "dense":
-            d.ffn, d.ff, d.limit = _lib.FL_FFN["dense"], int(mlp["ff"]), float(mlp["limit"])
-        elif mlp["kind"] == "moe":
-            d.ffn, d.ff, d.limit = _lib.FL_FFN["moe"], int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
-            d.experts, d.top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
-            if mlp.get("shared"):
-                d.shared_ff, d.shared_limit = int(mlp["shared"]["ff"]), float(mlp["shared"]["limit"])
-        else:
-            raise FastllmError(-1, f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+            _rotary_desc(d, m.get("rot") or {}, d.rot_dim)
+        _ffn_desc(d, i, l.get("mlp"))
     return arr
 
 
-class NifunexWithConfig(_CausalBase):
-    """The layered decoder (no reference path): gated-linear-attention and windowed latent-attention layers, dense / MoE
-    feed-forward, norms before and after every sublayer.  `config` is the parsed config.json (a dict: vocab, width, norm.eps and
-    one entry per layer).  Positions are the caller's, as for Llama; the device cache hands out pages on demand and keeps a
-    recurrent-state slot per sequence."""
-    arch, family, architectures = "nifunex", "Nifunex", ("Nifunex",)
+def _ffn_desc(d, i: int, mlp, act: str = "swish_clamp", bias: bool = False):
+    """fills the feed-forward fields of a FlLayerDesc from a layer's 'mlp' entry (None = the layer has none)"""
+    d.ffn_act, d.ffn_bias = _lib.FL_ACT[act], 1 if bias else 0
+    if not mlp:
+        d.ffn = _lib.FL_FFN["none"]
+    elif mlp["kind"] == "dense":
+        d.ffn, d.ff, d.limit = _lib.FL_FFN["dense"], int(mlp["ff"]), float(mlp.get("limit", 0.0))
+    elif mlp["kind"] == "moe":
+        d.ffn, d.ff, d.limit = _lib.FL_FFN["moe"], int(mlp["expert"]["ff"]), float(mlp["expert"]["limit"])
+        d.experts, d.top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
+        if mlp.get("shared"):
+            d.shared_ff, d.shared_limit = int(mlp["shared"]["ff"]), float(mlp["shared"]["limit"])
+    else:
+        raise FastllmError(-1, f"layer {i}: unknown feed-forward kind {mlp['kind']!r}")
+
+
+def _rotary_desc(d, rot: dict, default_dims: int):
+    """fills the rotary fields (leading rotated channels, base, optional YaRN scaling) from a mixer's 'rot' entry"""
+    d.rot_dims = int(rot.get("dims", default_dims))
+    d.rot_base = float(rot.get("base", 10000.0))
+    sc = rot.get("scaling")
+    if sc:
+        d.yarn_factor, d.yarn_original = float(sc["factor"]), float(sc["original"])
+        d.yarn_fast, d.yarn_slow = float(sc["fast"]), float(sc["slow"])
+
+
+class _LayeredBase(_CausalBase):
+    """Adapters of the layered decoders: `config` is the parsed config.json (a dict: vocab, width, norm.eps and one entry per
+    layer).  A subclass names its architecture, its norm conventions and how a layer entry becomes a FlLayerDesc.  Positions are
+    the caller's, as for Llama; the device cache hands out pages on demand and keeps a recurrent-state slot per sequence."""
     position_per_call = False
     MAX_BATCH = 1
     POOL_TOKENS = None          # None: room for MAX_BATCH x capacity tokens
+    norm_plain = False          # layer norms and the final norm scale by w instead of 1 + w
+    no_pre_norm = False         # sublayers read the residual stream itself; only their outputs are normed
 
     def __init__(self, dev: DeviceModel, cfg, config: dict):
         super().__init__(dev, cfg)
         self.config = config
 
     @classmethod
-    def initialize_model(cls, config: dict, tensors, dtype="bf16", device: int = 0, *, random_seed=None, std: float = 0.02, decay_rank=None):
-        """tensors: dict or iterable of (name, array) (f32 / f16 / uint16 bf16 bits), or None for synthetic weights (then
-        decay_rank gives the decay bottleneck's rows).  dtype "bf16": the serving precision; "f32": every product and the cache in
-        true 32-bit."""
+    def layer_descs(cls, config: dict, tensor_shapes: dict, **hints):
+        """config.json (+ the shapes of the checkpoint's tensors, for sizes the file does not spell out) -> ctypes array of FlLayerDesc"""
+        raise NotImplementedError
+
+    @classmethod
+    def initialize_model(cls, config: dict, tensors, dtype="bf16", device: int = 0, *, random_seed=None, std: float = 0.02, **hints):
+        """tensors: dict or iterable of (name, array) (f32 / f16 / uint16 bf16 bits), or None for synthetic weights.  dtype "bf16":
+        the serving precision; "f32": every product and the cache in true 32-bit."""
         if dtype not in ("bf16", "bfloat16", "f32", "float32"):
             raise FastllmError(-1, f"unsupported dtype {dtype!r}")
-        items = None
-        ranks = {}
+        items, shapes = None, {}
         if tensors is not None:
             items = list(tensors.items() if hasattr(tensors, "items") else tensors)
-            for name, arr in items:
-                if name.endswith(".mix.a1") and name[0] == "l":
-                    ranks[int(name[1:name.index(".")])] = int(np.asarray(arr).shape[0])
-        else:
-            ranks = {i: int(decay_rank or 16) for i, l in enumerate(config["layers"]) if l["type"] == "gla"}
+            shapes = {name: tuple(np.asarray(arr).shape) for name, arr in items}
         sc = _lib.FlStackConfig()
-        sc.arch = _lib.FL_ARCH["nifunex"]
+        sc.arch = _lib.FL_ARCH[cls.arch]
         sc.vocab, sc.width, sc.n_layers = int(config["vocab"]), int(config["width"]), len(config["layers"])
         sc.norm_eps = float(config["norm"]["eps"])
         sc.compute_dtype = _lib.FL_DTYPE_F32 if dtype in ("f32", "float32") else _lib.FL_DTYPE_BF16
-        dev = DeviceModel(sc, device, layers=nifunex_layer_descs(config, ranks))
+        sc.norm_plain, sc.no_pre_norm = int(cls.norm_plain), int(cls.no_pre_norm)
+        dev = DeviceModel(sc, device, layers=cls.layer_descs(config, shapes, **hints))
         if items is None:
             dev.random_init(0 if random_seed is None else random_seed, std)
         else:
             for name, arr in items:
                 a = np.asarray(arr)
                 if a.dtype.kind in "iu" and a.dtype != np.uint16:
-                    continue            # integer tables: this design reads none
+                    continue            # integer tables: these designs read none
                 dev.put_tensor(name, a)
         dev.finalize()
         self = cls(dev, sc, config)
@@ -593,13 +602,72 @@ class NifunexWithConfig(_CausalBase):
             cache.inner = self.new_device_cache(max(self.MAX_BATCH, ids.shape[0]))
         return cache.inner.forward(ids, pos)
 
-    def clone(self) -> "NifunexWithConfig":
-        return NifunexWithConfig(self.dev.clone(), self.cfg, self.config)
+    def clone(self):
+        return type(self)(self.dev.clone(), self.cfg, self.config)
+
+
+class NifunexWithConfig(_LayeredBase):
+    """The Nifunex decoder (no reference path): gated-linear-attention and windowed latent-attention layers, dense / MoE
+    feed-forward, norms with a zero-centred weight before and after every sublayer."""
+    arch, family, architectures = "nifunex", "Nifunex", ("Nifunex",)
+
+    @classmethod
+    def layer_descs(cls, config: dict, tensor_shapes: dict, decay_rank=None):
+        """the decay bottleneck's rows are the one size config.json does not spell out: the first dimension of 'l<i>.mix.a1', or
+        decay_rank for synthetic weights"""
+        ranks = {}
+        for name, shp in tensor_shapes.items():
+            if name.endswith(".mix.a1") and name[0] == "l":
+                ranks[int(name[1:name.index(".")])] = int(shp[0])
+        if not tensor_shapes:
+            ranks = {i: int(decay_rank or 16) for i, l in enumerate(config["layers"]) if l["type"] == "gla"}
+        return nifunex_layer_descs(config, ranks)
+
+
+def rofetar_layer_descs(config: dict):
+    """config.json of the Rofetar decoder -> ctypes array of FlLayerDesc (every size and constant comes from the file)."""
+    layers = config["layers"]
+    arr = (_lib.FlLayerDesc * len(layers))()
+    for i, l in enumerate(layers):
+        d, m, kind = arr[i], l["mixer"], l["type"]
+        if kind not in ("attention", "mamba2", "delta"):
+            raise FastllmError(-1, f"layer {i}: unknown mixer type {kind!r}")
+        d.mixer = _lib.FL_MIXER[kind]
+        d.heads, d.vdim = int(m["heads"]), int(m["vdim"])
+        d.kv_from = -1
+        if kind == "attention":
+            d.dim, d.kv_heads = int(m["dim"]), int(m.get("kv_heads") or m["heads"])
+            d.kv_from = int(m["kv_from"]) if m.get("kv_from") is not None else -1
+            d.scale = float(m["scale"])
+            d.softcap = float(m.get("softcap") or 0.0)
+            d.sink, d.rot_halves = 1, 1
+            _rotary_desc(d, m.get("rot") or {"dims": 0}, 0)
+        elif kind == "mamba2":
+            d.state, d.groups, d.conv = int(m["state"]), int(m.get("groups") or 1), int(m["conv"])
+            d.norm_groups = int(m.get("norm_groups") or 1)
+        else:
+            d.dim, d.kv_heads, d.conv = int(m["dim"]), int(m.get("kv_heads") or m["heads"]), int(m["conv"])
+        _ffn_desc(d, i, l.get("mlp"), act="gelu_tanh", bias=True)
+        if d.ffn == _lib.FL_FFN["moe"]:
+            raise FastllmError(-1, f"layer {i}: this design has dense feed-forwards only")
+    return arr
+
+
+class RofetarWithConfig(_LayeredBase):
+    """The Rofetar decoder (no reference path): grouped-query attention with per-head q/k norms, a score cap and a softmax sink
+    (optionally on another layer's keys and values), Mamba-2 and gated-delta-rule layers, a biased tanh-gelu feed-forward; a
+    sublayer reads the residual stream as it is and only its output is normed (plain weight)."""
+    arch, family, architectures = "rofetar", "Rofetar", ("Rofetar",)
+    norm_plain, no_pre_norm = True, True
+
+    @classmethod
+    def layer_descs(cls, config: dict, tensor_shapes: dict):
+        return rofetar_layer_descs(config)
 
 
 # every adapter, in the order the registry tries them (model_registry.rs:169-182 keeps the same kind of list)
 def registered_models():
-    return (LlamaWithConfig, MistralWithConfig, QwenWithConfig, MixtralWithConfig, NifunexWithConfig)
+    return (LlamaWithConfig, MistralWithConfig, QwenWithConfig, MixtralWithConfig, NifunexWithConfig, RofetarWithConfig)
 
 
 def model_class_for(config: dict):
@@ -620,7 +688,7 @@ def load_model(model_dir: str, dtype: str = "bf16", device: int = 0):
     with open(os.path.join(model_dir, "config.json")) as f:
         config = json.load(f)
     cls = model_class_for(config)
-    if cls is NifunexWithConfig:
+    if issubclass(cls, _LayeredBase):
         return cls.initialize_model(config, safetensors_io.iter_tensors(model_dir, copy=True), dtype, device)
     cf = ConfigFile(config["hidden_size"], config["intermediate_size"], config["vocab_size"], config["num_hidden_layers"],
                     config["num_attention_heads"], config.get("num_key_value_heads"), config.get("rms_norm_eps", 1e-5),

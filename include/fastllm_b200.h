@@ -68,8 +68,10 @@ typedef enum fl_arch {
     FL_ARCH_QWEN2 = 2,     /* Qwen2ForCausalLM, qkv bias (models/qwen.rs)    */
     FL_ARCH_MIXTRAL = 3,   /* MixtralForCausalLM top-k MoE (no reference path; candle mixtral.rs) */
     FL_ARCH_BERT = 4,      /* BertModel encoder         (models/embeddings.rs) */
-    FL_ARCH_NIFUNEX = 5    /* layered decoder described by fl_layer_desc (no reference path): gated-linear-attention and windowed
+    FL_ARCH_NIFUNEX = 5,   /* layered decoder described by fl_layer_desc (no reference path): gated-linear-attention and windowed
                               latent-attention mixers, dense / mixture-of-experts feed-forward, a norm before and after each sublayer */
+    FL_ARCH_ROFETAR = 6    /* layered decoder (no reference path): grouped-query attention with a softmax sink, Mamba-2 and gated-delta-rule
+                              mixers, biased gelu feed-forward; only the OUTPUT of a sublayer is normed (fl_stack_config.no_pre_norm) */
 } fl_arch;
 
 typedef enum fl_dtype { FL_DTYPE_F32 = 0, FL_DTYPE_BF16 = 1, FL_DTYPE_F16 = 2 } fl_dtype;
@@ -110,11 +112,29 @@ typedef struct fl_config {
  *                         rotary embedding with optional YaRN frequency scaling, sliding window (`window` keys, 0 = none), plain
  *                         softmax with the given `scale`.  kv_from >= 0: the layer reads layer kv_from's cached latent instead of
  *                         projecting its own.
- * Feed-forward: y = W_down (g * sigmoid(1.702 g) * (u + 1)), g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit); dense, or
- * `top` of `experts` such experts weighted by their renormalised softmax scores plus an optional always-on shared expert scaled by
- * sigmoid(w_sg . h). */
-typedef enum fl_mixer_kind { FL_MIXER_GLA = 0, FL_MIXER_LATENT_ATTN = 1 } fl_mixer_kind;
+ *   FL_MIXER_ATTN         grouped-query softmax attention over a paged key/value cache: `heads` query heads share `kv_heads` key/value
+ *                         heads (query head h reads key/value head h / (heads / kv_heads)); queries and keys are RMS-normed per head
+ *                         (one weight of `dim` entries for all heads) and then turned by a rotary embedding on their first rot_dims
+ *                         channels (pairs (i, i + rot_dims/2) when rot_halves, else (2i, 2i+1)); score = q.k * scale, optionally
+ *                         squashed to softcap * tanh(score / softcap); `sink` adds 1 to the softmax denominator (a valueless key of
+ *                         score 0).  window as for latent attention.  kv_from >= 0: the layer reads layer kv_from's cached keys and
+ *                         values (as cached: normed and rotated) and projects only queries.
+ *   FL_MIXER_MAMBA2       Mamba-2 state-space layer: W_in h = [z | x | B | C | dt] (inner = heads * vdim, `groups` x `state` for B and
+ *                         C); x|B|C pass a causal per-channel convolution of `conv` taps with bias, then silu; dt = softplus(dt + bias);
+ *                         per head an f32 state S [state, vdim]: S <- exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x; y * silu(z) is
+ *                         RMS-normed in `norm_groups` equal parts, scaled by a weight and projected.
+ *   FL_MIXER_DELTA        gated delta rule: q, k (kv_heads x dim) and v (heads x vdim) pass a bias-free causal convolution of `conv`
+ *                         taps and silu; q and k become unit vectors per head (q also times dim^-1/2); beta = sigmoid(W_b h), decay
+ *                         g = exp(-exp(A_log) softplus(W_a h + dt_bias)) per head; per head an f32 state S [dim, vdim]: S <- g S,
+ *                         u = beta (v - S^T k), S <- S + k u^T, o = S^T q; o is RMS-normed per head, gated by silu(W_g h), projected.
+ * The recurrent mixers keep, per sequence slot, the state S and the last conv - 1 inputs of every convolved channel.
+ * Feed-forward (ffn_act = FL_ACT_SWISH_CLAMP): y = W_down (g * sigmoid(1.702 g) * (u + 1)), g = min(W_gate h, limit), u = clamp(W_up h,
+ * -limit, limit); (ffn_act = FL_ACT_GELU_TANH): y = W_down (gelu_tanh(W_gate h) * (W_up h)); ffn_bias adds a bias to all three
+ * projections.  Dense, or `top` of `experts` such experts weighted by their renormalised softmax scores plus an optional always-on
+ * shared expert scaled by sigmoid(w_sg . h). */
+typedef enum fl_mixer_kind { FL_MIXER_GLA = 0, FL_MIXER_LATENT_ATTN = 1, FL_MIXER_ATTN = 2, FL_MIXER_MAMBA2 = 3, FL_MIXER_DELTA = 4 } fl_mixer_kind;
 typedef enum fl_ffn_kind { FL_FFN_NONE = 0, FL_FFN_DENSE = 1, FL_FFN_MOE = 2 } fl_ffn_kind;
+typedef enum fl_ffn_act { FL_ACT_SWISH_CLAMP = 0, FL_ACT_GELU_TANH = 1 } fl_ffn_act;
 
 typedef struct fl_layer_desc {
     int32_t mixer;                     /* fl_mixer_kind */
@@ -135,7 +155,14 @@ typedef struct fl_layer_desc {
     int32_t experts, top;              /* MoE */
     int32_t shared_ff;                 /* MoE: hidden width of the shared expert, 0 = none */
     float shared_limit;
-    int32_t reserved[4];
+    int32_t kv_heads;                  /* attention / delta rule: key (and query, for the delta rule) heads; 0 = heads */
+    int32_t conv;                      /* Mamba-2 / delta rule: taps of the short causal convolution */
+    int32_t state, groups, norm_groups;/* Mamba-2: state size per head, B / C groups, parts of the gated output norm */
+    float softcap;                     /* attention: score <- softcap * tanh(score / softcap); 0 = none */
+    int32_t sink;                      /* attention: 1 = one is added to the softmax denominator */
+    int32_t rot_halves;                /* attention: 1 = rotary pairs are (i, i + rot_dims / 2), 0 = (2i, 2i + 1) */
+    int32_t ffn_act, ffn_bias;         /* dense feed-forward: fl_ffn_act; 1 = gate / up / down carry biases */
+    int32_t reserved[6];
 } fl_layer_desc;
 
 typedef struct fl_stack_config {
@@ -144,7 +171,10 @@ typedef struct fl_stack_config {
     float norm_eps;
     int32_t compute_dtype;             /* FL_DTYPE_BF16: bf16 weights on the tensor-core path, bf16 cache; FL_DTYPE_F32: every product
                                           and the cache in true 32-bit (weights are still stored as the bf16 values they were given) */
-    int32_t reserved[6];
+    int32_t norm_plain;                /* 0: the layer norms and the final norm scale by (1 + w);  1: by w */
+    int32_t no_pre_norm;               /* 0: x += norm_b(sub(norm_a(x)));  1: x += norm(sub(x)) -- sublayers read the residual stream itself
+                                          and "l<i>.norm1" / "l<i>.norm2" name the norms of the mixer's / feed-forward's output */
+    int32_t reserved[4];
 } fl_stack_config;
 
 /* ---- process / device -------------------------------------------------------------------------- */
@@ -156,7 +186,8 @@ FL_EXPORT int fl_device_synchronize(void);
 /* ---- model (weights) --------------------------------------------------------------------------- */
 FL_EXPORT int fl_model_create(const fl_config* cfg, fl_model** out);
 /* A layered model: cfg->n_layers entries of `layers`.  Tensors then arrive by name through fl_model_put_tensor ("embed", "head",
- * "final.norm", "l<i>.norm1|norm1b|norm2|norm2b", "l<i>.mix.*", "l<i>.mlp.*"); fl_model_finalize checks that all came. */
+ * "final.norm", "l<i>.norm1|norm1b|norm2|norm2b" (no_pre_norm: "l<i>.norm1|norm2"), "l<i>.mix.*", "l<i>.mlp.*"); fl_model_finalize
+ * checks that all came. */
 FL_EXPORT int fl_model_create_layered(const fl_stack_config* cfg, const fl_layer_desc* layers, fl_model** out);
 /* Upload one tensor by its HuggingFace name (same names VarBuilder asks for).  f32/f16 inputs are rounded to
  * bf16 (round-to-nearest-even), as VarBuilder::from_tensors(.., DType::BF16, ..) does (main.rs:120).  The host
