@@ -553,10 +553,14 @@ static void ensure_ws(fl_cache& c, size_t T, size_t n_want) {
     }
 }
 
+// The FMA-chain GEMM: f32 accumulators where it stands in for the tensor-core GEMM on shapes outside its tiles (serving precision),
+// f64 accumulators in the exact mode.
 static void gemm(LaunchCtx& lc, const char* tag, const float* A, int lda, const uint16_t* Wt, int N, int K, float* Y, int ldy, int R) {
     if (R <= 0) return;
     LyGemm g{A, 0, lda, nullptr, Wt, 0, N, K, Y, 0, ldy, nullptr, R};
-    launch(lc, tag, (uint64_t)N * K * 2, ly_gemm_kernel, dim3((N + kLyBN - 1) / kLyBN, (R + kLyBM - 1) / kLyBM, 1), dim3(256), 0, g);
+    const dim3 grid((N + kLyBN - 1) / kLyBN, (R + kLyBM - 1) / kLyBM, 1);
+    if (lc.exact) launch(lc, tag, (uint64_t)N * K * 2, ly_gemm_kernel<double>, grid, dim3(256), 0, g);
+    else launch(lc, tag, (uint64_t)N * K * 2, ly_gemm_kernel<float>, grid, dim3(256), 0, g);
 }
 // Y[R, N] = A[R, K] . Wt[N, K]^T on the tensor cores when the matrix has a descriptor (serving precision; A as hi | lo halves),
 // else on the exact kernel.  Split-K slices of the tensor-core GEMM are folded in slice order.
@@ -579,8 +583,9 @@ static void gemm_tc_or_exact(fl_cache& c, LaunchCtx& lc, const char* tag, const 
 
 static void gemm_groups(LaunchCtx& lc, const char* tag, const LyGemm& g, int groups, int max_rows) {
     if (max_rows <= 0) return;
-    launch(lc, tag, (uint64_t)groups * g.N * g.K * 2, ly_gemm_kernel, dim3((g.N + kLyBN - 1) / kLyBN, (max_rows + kLyBM - 1) / kLyBM, groups),
-           dim3(256), 0, g);
+    const dim3 grid((g.N + kLyBN - 1) / kLyBN, (max_rows + kLyBM - 1) / kLyBM, groups);
+    if (lc.exact) launch(lc, tag, (uint64_t)groups * g.N * g.K * 2, ly_gemm_kernel<double>, grid, dim3(256), 0, g);
+    else launch(lc, tag, (uint64_t)groups * g.N * g.K * 2, ly_gemm_kernel<float>, grid, dim3(256), 0, g);
 }
 
 template <typename CT>
@@ -738,6 +743,7 @@ void layered_forward(fl_cache& c, const int* slots, const int* counts, int n, co
     LaunchCtx lc;
     lc.stream = c.stream;
     lc.pdl = false;
+    lc.exact = m.f32;
     // A step in which every sequence brings ONE token has a launch geometry that depends on (sequences, wanted rows) alone --
     // positions, slots and pages are read from the device tables -- so it is captured into a CUDA graph the second time the pair is
     // seen and replayed from then on (FL_NO_GRAPH=1 keeps eager launches).

@@ -156,6 +156,8 @@ struct LyGemm {
 };
 constexpr int kLyBM = 64, kLyBN = 64, kLyBK = 16;
 
+// Acc = double (the exact mode): every output is the correctly rounded f32 of its dot product, whatever K.
+template <typename Acc>
 static __global__ void __launch_bounds__(256) ly_gemm_kernel(LyGemm g) {
     __shared__ float As[kLyBK][kLyBM + 4];
     __shared__ float Ws[kLyBK][kLyBN + 4];
@@ -174,7 +176,7 @@ static __global__ void __launch_bounds__(256) ly_gemm_kernel(LyGemm g) {
     const float* arow = nullptr;
     if (ap < p_hi) arow = A + (size_t)(g.a_idx ? g.a_idx[ap] : ap) * g.lda;
     const uint16_t* wrow = (n0 + lr < g.N) ? Wm + (size_t)(n0 + lr) * g.K : nullptr;
-    float acc[4][4] = {};
+    Acc acc[4][4] = {};
     for (int k0 = 0; k0 < g.K; k0 += kLyBK) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -191,7 +193,7 @@ static __global__ void __launch_bounds__(256) ly_gemm_kernel(LyGemm g) {
 #pragma unroll
             for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+                for (int j = 0; j < 4; ++j) acc[i][j] = fma((Acc)a[i], (Acc)b[j], acc[i][j]);
         }
         __syncthreads();
     }
@@ -202,7 +204,7 @@ static __global__ void __launch_bounds__(256) ly_gemm_kernel(LyGemm g) {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx * 4 + j;
-            if (n < g.N) Y[(size_t)p * g.ldy + n] = acc[i][j];
+            if (n < g.N) Y[(size_t)p * g.ldy + n] = (float)acc[i][j];
         }
     }
 }

@@ -37,6 +37,7 @@ struct LaunchCtx {
     bool pdl = true;          // programmatic dependent launch on every kernel of the step
     bool capturing = false;   // inside cudaStreamBeginCapture: no events, no profile
     uint64_t captured = 0;    // kernels recorded into the graph being captured
+    bool exact = false;       // layered models, exact mode: the FMA-chain GEMM accumulates in f64
 };
 
 // Launches `kern` with optional PDL.  `tag`/`bytes` feed the per-kernel profile (algorithmic bytes of that launch).
