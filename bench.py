@@ -52,6 +52,9 @@ WORKLOADS = {
     "qwen25_7b_prefill4k": ("qwen25_7b", 1, 4096, "Qwen2.5-7B bf16 prefill 4096 tokens (+ 256 decode steps reported beside it)"),
     "nifunex_vs_mixtral": ("nifunex", 8, 2048, "layered decoder (Nifunex: GLA + windowed latent attention + MoE with shared expert) beside Mixtral "
                            "at equal width / experts / layers: 2048-token prefill and batch-8 decode at 2k context, random weights"),
+    "rofetar_vs_nifunex": ("rofetar", 8, 2048, "layered decoder (Rofetar: gated delta rule + grouped-query attention with sink + Mamba-2, dense gelu "
+                           "feed-forward) beside Nifunex (GLA + latent attention, dense feed-forward) and Mistral at equal width / ff / layers: "
+                           "2048-token prefill and batch-8 decode at 2k context, random weights"),
 }
 QWEN_PREFILL_TFLOP_4K = 56.83         # 53.46 linear + 3.37 causal attention
 MINILM_FLOP_PER_TOKEN = 22.41e6      # 2 x 10.617 M linear + 4 T H 6 attention at T = 128
@@ -345,7 +348,7 @@ def run_reference(args, rank):
     if rank != 0:
         return
     arch, batch, ctx, desc = WORKLOADS[args.workload]
-    if args.workload in ("mixtral8x7b_b32", "qwen25_7b_prefill4k", "nifunex_vs_mixtral"):
+    if args.workload in ("mixtral8x7b_b32", "qwen25_7b_prefill4k", "nifunex_vs_mixtral", "rofetar_vs_nifunex"):
         print(json.dumps({"impl": "reference", "unavailable": f"no CPU leg for workload {args.workload}: the reference does not wire Mixtral "
                           "and a 4096-token f32 prefill of a 7B model does not fit a bounded CPU sample; the decode workloads carry the CPU baseline"}),
               flush=True)
@@ -962,6 +965,122 @@ def run_layered_compare(args, local_rank):
                       "clocks": clk.summary(t_wall0, t_wall1), "sizes": results}), flush=True)
 
 
+def _rofetar_config(width, ff, layers, vocab):
+    """A Rofetar config at the sizes of a real model's layers: heads of 128 channels; per four layers a gated-delta-rule layer, an
+    attention layer (4 query heads per key/value head), a Mamba-2 layer (inner width 2 x width in heads of 64, state 128) and an
+    attention layer on the first one's keys and values; a dense feed-forward after every mixer."""
+    H = width // 128
+    rot = {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+    ly = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff}
+        if i % 4 == 0:
+            ly.append({"type": "delta", "mixer": {"heads": H, "kv_heads": max(1, H // 2), "dim": 128, "vdim": 128, "conv": 4}, "mlp": mlp})
+        elif i % 4 == 2:
+            ly.append({"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": max(1, H // 4), "norm_groups": 1, "conv": 4},
+                       "mlp": mlp})
+        else:
+            m = {"heads": H, "kv_heads": max(1, H // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0, "rot": rot}
+            if i % 4 == 3:
+                m["kv_from"] = i - 2
+            ly.append({"type": "attention", "mixer": m, "mlp": mlp})
+    return {"architecture": "Rofetar", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": ly}
+
+
+def _nifunex_dense_config(width, ff, layers, vocab):
+    """The Nifunex layers of _nifunex_config with a dense feed-forward and no window: the closest existing design at equal sizes."""
+    cfg = _nifunex_config(width, ff, layers, vocab, 0)
+    for l in cfg["layers"]:
+        l["mlp"] = {"kind": "dense", "ff": ff, "limit": 7.0}
+        l["mixer"].pop("mask", None)
+    return cfg
+
+
+def run_rofetar_compare(args, local_rank):
+    """--workload rofetar_vs_nifunex (one GPU): Rofetar, Nifunex (dense feed-forward) and Mistral at the same width / ff / layer count,
+    random weights -- one 2048-token prefill and batch-8 decode steps at a 2k context, through the public calls (host ids in,
+    logits out), with the per-kernel CUDA-event profile of one call of each kind."""
+    import torch
+    from fastllm_b200 import models
+    batch, T, steps, warm = 8, 2048, max(4, min(args.steps, 32)), 3
+    sizes = [("w1024", 1024, 2816, 4), ("w2048", 2048, 5632, 4), ("w4096", 4096, 14336, 4)]
+    vocab = 32000
+    results = {}
+
+    def timed(fn, n):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / n
+
+    def layered(cls, cfg, **hints):
+        model, _ = cls.initialize_model(cfg, None, "bf16", local_rank, random_seed=0, std=0.02, **hints)
+        cache = model.new_device_cache(max_batch=batch, max_seq=T + 64, pool_tokens=batch * (T + 64))
+        ids = (np.arange(T, dtype=np.uint64) * 7919 % (vocab - 5) + 3).astype(np.uint32)
+
+        def prefill():
+            cache.slot_reset(0)
+            cache.forward_ragged([0], [ids], None)
+        dt_p = timed(prefill, max(2, steps // 4))
+        models.prof_begin(); prefill(); prof_p = models.prof_end()
+        for s in range(1, batch):
+            cache.forward_ragged([s], [ids], None)
+        slots = list(range(batch))
+
+        def decode():
+            cache.forward_ragged(slots, [[7 + s] for s in slots], None)
+        dt_d = timed(decode, steps)
+        models.prof_begin(); decode(); prof_d = models.prof_end()
+        return {"prefill_tok_s": T / dt_p, "prefill_ms": dt_p * 1e3, "decode_tok_s": batch / dt_d, "decode_ms_per_step": dt_d * 1e3,
+                "weight_bytes": model.dev.streamed_bytes(), "prefill_kernels": _profile_table(prof_p), "decode_kernels": _profile_table(prof_d)}
+
+    with ClockSampler(local_rank) as clk:
+        t_wall0 = time.time()
+        for name, width, ff, layers in sizes:
+            rec = {"width": width, "ff": ff, "layers": layers}
+            rec["rofetar"] = layered(models.RofetarWithConfig, _rofetar_config(width, ff, layers, vocab))
+            rec["nifunex"] = layered(models.NifunexWithConfig, _nifunex_dense_config(width, ff, layers, vocab), decay_rank=64)
+            cf = models.ConfigFile(width, ff, vocab, layers, width // 128, max(1, width // 512), 1e-5, 1e6, 32768, 32768)
+            mx, _ = models.MistralWithConfig.initialize_model(cf, None, "bf16", local_rank, random_seed=0, std=0.02)
+            mc = models.DeviceCache(mx.dev, batch, T + 64)
+            ids2 = (np.arange(T, dtype=np.uint64) * 7919 % (vocab - 5) + 3).astype(np.uint32)[None]
+            slots = list(range(batch))
+
+            def prefill_m():
+                mc.reset()
+                mc.forward_slots([0], ids2, [0])
+            dt_pm = timed(prefill_m, max(2, steps // 4))
+            models.prof_begin(); prefill_m(); prof_pm = models.prof_end()
+            for s in range(1, batch):
+                mc.forward_slots([s], ids2, [0])
+            pos = [T] * batch
+
+            def decode_m():
+                mc.forward_slots(slots, np.asarray([[7 + s] for s in slots], dtype=np.uint32), pos)
+                for i in range(batch):
+                    pos[i] += 1
+            dt_dm = timed(decode_m, steps)
+            models.prof_begin(); decode_m(); prof_dm = models.prof_end()
+            rec["mistral"] = {"prefill_tok_s": T / dt_pm, "prefill_ms": dt_pm * 1e3, "decode_tok_s": batch / dt_dm, "decode_ms_per_step": dt_dm * 1e3,
+                              "weight_bytes": mx.dev.streamed_bytes(), "prefill_kernels": _profile_table(prof_pm), "decode_kernels": _profile_table(prof_dm)}
+            del mc, mx
+            results[name] = rec
+        t_wall1 = time.time()
+        time.sleep(0.12)
+    big = results[sizes[-1][0]]
+    print(json.dumps({"metric": "decode_tokens_per_s", "value": big["rofetar"]["decode_tok_s"], "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
+                      "ms_per_step": big["rofetar"]["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                      "data": "synthetic",
+                      "config": {"workload": WORKLOADS[args.workload][3], "batch": batch, "context": T, "timing": "wall clock around the public call "
+                                 "(host ids in, f32 logits out) with a device synchronise on both sides; per-kernel figures are CUDA events",
+                                 "l2": "weights of a step exceed L2 at every size"},
+                      "clocks": clk.summary(t_wall0, t_wall1), "sizes": results}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -995,6 +1114,9 @@ def main():
     if args.workload == "nifunex_vs_mixtral":
         if rank == 0:
             run_layered_compare(args, local_rank)
+    elif args.workload == "rofetar_vs_nifunex":
+        if rank == 0:
+            run_rofetar_compare(args, local_rank)
     elif args.workload == "minilm_256x128":
         run_minilm(args, rank, world, local_rank)
     elif args.workload == "qwen25_7b_prefill4k":

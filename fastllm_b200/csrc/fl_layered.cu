@@ -678,9 +678,60 @@ static void latent_attn_tc(fl_cache& c, LaunchCtx& lc, const LayeredLayerW& lw, 
         const CUtensorMap tk = make_tmap_bf16(y.at_kc.p, (uint64_t)nkp, (uint64_t)Ep, (uint64_t)Ep, 128);
         dense_gemm(c, lc, "gemm_tc_attn_scores", rows, nkp, Ep, tk, y.at_s.p, y.at_qhi.p, y.at_qlo.p);
         launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), 0, (const float*)y.at_s.p, a.row_pos, r0 + f, H, k_lo, nk, nkp, a.window,
-               y.at_phi.p, y.at_plo.p);
+               0.f, 0, y.at_phi.p, y.at_plo.p);
         const CUtensorMap tv = make_tmap_bf16(y.at_kct.p, (uint64_t)C, (uint64_t)nkp, (uint64_t)nkp, 128);
         dense_gemm(c, lc, "gemm_tc_attn_values", rows, C, nkp, tv, a.ol + (size_t)(r0 + f) * H * C, y.at_phi.p, y.at_plo.p);
+    }
+}
+
+// Grouped-query attention of rows [r0, r0 + Ts) -- one sequence's portion, positions pos0.. -- on the tensor-core GEMM: per block of
+// query rows and per key/value head a score GEMM whose rows are (token, query head of the group) pairs, an f32 softmax (score cap,
+// sink, causal mask) and a value GEMM; the block size keeps a score block within a fixed scratch budget.
+static void gqa_attn_tc(fl_cache& c, LaunchCtx& lc, const GqaAttnArgs& a, int r0, int Ts, int pos0, int slot) {
+    LayeredCache& y = *c.ly;
+    const int H = a.H, G = a.G, rep = H / G, D = a.D, Dv = a.Dv, Dp = (D + 63) / 64 * 64, E = G * (D + Dv);
+    const size_t budget = (size_t)48 << 20;                // floats in a score block (192 MB); P halves take the same again
+    auto keys_for = [&](int qb, int first) {
+        const int p_lo = pos0 + first, p_hi = pos0 + std::min(Ts, first + qb);
+        const int k_lo = (a.window > 0 && p_lo - a.window + 1 > 0) ? p_lo - a.window + 1 : 0;
+        return ((p_hi - k_lo) + 63) / 64 * 64;
+    };
+    int qb = 1024;
+    while (qb > 8 && (size_t)qb * rep * keys_for(qb, std::max(0, Ts - qb)) > budget) qb /= 2;
+    const size_t rows_max = (size_t)std::min(qb, Ts) * rep;
+    size_t nkp_max = 0;
+    for (int f = 0; f < Ts; f += qb) nkp_max = std::max<size_t>(nkp_max, keys_for(qb, f));
+    auto need = [&](auto& buf, size_t n) { if (buf.n < n) { FL_CUDA(cudaStreamSynchronize(c.stream)); buf.alloc(n + n / 4); } };
+    need(y.at_kc, nkp_max * Dp); need(y.at_kct, (size_t)Dv * nkp_max);
+    need(y.at_qhi, rows_max * Dp); need(y.at_qlo, rows_max * Dp);
+    need(y.at_s, rows_max * nkp_max); need(y.at_phi, rows_max * nkp_max); need(y.at_plo, rows_max * nkp_max);
+    need(y.at_o, rows_max * G * Dv);
+    const int* page_row = y.page_table.p + (size_t)slot * c.pages_per_seq;
+    for (int f = 0; f < Ts; f += qb) {
+        const int nq = std::min(qb, Ts - f), p_lo = pos0 + f, p_hi = p_lo + nq;
+        const int k_lo = (a.window > 0 && p_lo - a.window + 1 > 0) ? p_lo - a.window + 1 : 0, nk = p_hi - k_lo, nkp = (nk + 63) / 64 * 64;
+        const int rows = nq * rep;
+        if (rows <= 128) {          // a short tail: the per-(row, head) kernel
+            GqaAttnArgs t = a;
+            t.row_base = r0 + f;
+            launch_gqa_attn<uint16_t>(lc, t, nq);
+            continue;
+        }
+        for (int g = 0; g < G; ++g) {
+            launch(lc, "gqa_gather_kv", 0, ly_gqa_gather_kv_kernel, dim3(nkp), dim3(128), 0, (const uint16_t*)a.pool, page_row, k_lo, nk, nkp, E, g * D, D, Dp,
+                   G * D + g * Dv, Dv, y.at_kc.p, y.at_kct.p);
+            launch(lc, "gqa_build_q", 0, ly_gqa_build_q_kernel, dim3(nq, rep), dim3(128), 0, a.proj, a.ldp, a.off_q, r0 + f, rep, g, D, Dp, a.scale, y.at_qhi.p,
+                   y.at_qlo.p);
+            const CUtensorMap tk = make_tmap_bf16(y.at_kc.p, (uint64_t)nkp, (uint64_t)Dp, (uint64_t)Dp, 128);
+            dense_gemm(c, lc, "gemm_tc_attn_scores", rows, nkp, Dp, tk, y.at_s.p, y.at_qhi.p, y.at_qlo.p);
+            launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), 0, (const float*)y.at_s.p, a.row_pos, r0 + f, rep, k_lo, nk, nkp, a.window,
+                   a.softcap, a.sink, y.at_phi.p, y.at_plo.p);
+            const CUtensorMap tv = make_tmap_bf16(y.at_kct.p, (uint64_t)Dv, (uint64_t)nkp, (uint64_t)nkp, 128);
+            dense_gemm(c, lc, "gemm_tc_attn_values", rows, Dv, nkp, tv, y.at_o.p + (size_t)g * rows * Dv, y.at_phi.p, y.at_plo.p);
+        }
+        const size_t no = (size_t)nq * H * Dv;
+        launch(lc, "gqa_scatter", 0, ly_gqa_scatter_kernel, dim3((unsigned)std::min<size_t>(4 * kNumSMs, (no + 255) / 256)), dim3(256), 0, (const float*)y.at_o.p, nq,
+               G, rep, Dv, r0 + f, a.out, a.ohi, a.olo);
     }
 }
 
@@ -817,7 +868,24 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti), dim3(128), psm, pa);
             GqaAttnArgs at{y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot,
                            y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0};
-            if (m.f32) launch_gqa_attn<float>(lc, at, Ti); else launch_gqa_attn<uint16_t>(lc, at, Ti);
+            // long portions (serving precision): scores and weighted sums as tensor-core GEMMs; decoded tokens, short portions and
+            // the exact mode on the per-(row, head) kernel.  Rows are taken in order.
+            static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
+            int done = 0;
+            for (int si = 0; si < n; ++si) {
+                const int r0 = h_row0[si], Ts = counts[si];
+                if (m.f32 || tc_attn_off || Dv % 8 != 0 || Ts < 64 || (long long)Ts * (H / G) <= 128) continue;
+                if (r0 > done) {
+                    at.row_base = done;
+                    launch_gqa_attn<uint16_t>(lc, at, r0 - done);
+                }
+                gqa_attn_tc(c, lc, at, r0, Ts, h_pos0[si], slots[si]);
+                done = r0 + Ts;
+            }
+            if (done < Ti) {
+                at.row_base = done;
+                if (m.f32) launch_gqa_attn<float>(lc, at, Ti - done); else launch_gqa_attn<uint16_t>(lc, at, Ti - done);
+            }
         } else if (d.mixer == FL_MIXER_MAMBA2 || d.mixer == FL_MIXER_DELTA) {
             const bool delta = d.mixer == FL_MIXER_DELTA;
             const int G = delta ? d.kv_heads : d.groups, rows = delta ? D : d.state;

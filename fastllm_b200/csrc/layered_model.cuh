@@ -114,7 +114,7 @@ struct LayeredCache {
     DevBuf<int> grp_cnt;
     // tensor-core latent attention of long portions: gathered keys, their transpose, Q / P operand halves, the score block
     DevBuf<uint16_t> at_kc, at_kct, at_qhi, at_qlo, at_phi, at_plo;
-    DevBuf<float> at_s;
+    DevBuf<float> at_s, at_o;           // at_o: grouped-query attention, the value GEMMs' outputs per key/value head before they are interleaved
 };
 
 void layered_build(LayeredModel& m, const fl_layer_desc* layers);

@@ -528,17 +528,20 @@ static __global__ void ly_attn_build_q_kernel(const float* __restrict__ qa, cons
         split_store(qhi, qlo, base + c, v);
     }
 }
-// P[r, col] = softmax over the keys the row's position admits (0 <= pos - j < window, j = k_lo + col), zero elsewhere; r = (token, head)
+// P[r, col] = softmax over the keys the row's position admits (0 <= pos - j < window, j = k_lo + col), zero elsewhere; row r belongs
+// to token r / H of the block.  softcap > 0: scores pass softcap * tanh(s / softcap) first; sink: the denominator gets exp(0) more.
 static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const int* __restrict__ row_pos, int row0, int H, int k_lo, int nk, int nkp,
-                                              int window, uint16_t* __restrict__ phi, uint16_t* __restrict__ plo) {
+                                              int window, float softcap, int sink, uint16_t* __restrict__ phi, uint16_t* __restrict__ plo) {
     __shared__ float red[33];
     const size_t r = blockIdx.x;
     const int pos = row_pos[row0 + (int)(r / H)];
     const int j_first = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     const int c_lo = j_first > k_lo ? j_first - k_lo : 0, c_hi = min(nk, pos - k_lo + 1);      // visible columns [c_lo, c_hi)
     const float* sr = S + r * nkp;
-    float m = -INFINITY;
-    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) m = fmaxf(m, sr[c]);
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    auto score = [&](int c) { const float v = sr[c]; return softcap > 0.f ? softcap * tanhf(v * inv_cap) : v; };
+    float m = sink ? 0.f : -INFINITY;
+    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) m = fmaxf(m, score(c));
     m = warp_max(m);
     {
         const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -549,10 +552,10 @@ static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const
         m = warp_max(t);
     }
     float sum = 0.f;
-    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) sum += expf(sr[c] - m);
-    const float inv = 1.f / block_sum(sum, red);
+    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) sum += expf(score(c) - m);
+    const float inv = 1.f / (block_sum(sum, red) + (sink ? expf(-m) : 0.f));
     for (int c = threadIdx.x; c < nkp; c += blockDim.x) {
-        const float p = (c >= c_lo && c < c_hi) ? expf(sr[c] - m) * inv : 0.f;
+        const float p = (c >= c_lo && c < c_hi) ? expf(score(c) - m) * inv : 0.f;
         split_store(phi, plo, r * nkp + c, p);
     }
 }
@@ -702,6 +705,45 @@ static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaA
         t *= inv;
         a.out[ob + c] = t;
         split_store(a.ohi, a.olo, ob + c, t);
+    }
+}
+
+// ---- grouped-query attention of long portions on the tensor-core GEMM (serving precision) ---------------------------------------
+// Per block of consecutive query rows of ONE sequence and per key/value head g: the keys the block can reach are gathered once
+// (Kc [nkp, Dp], zero padded) with the values transposed (Vt [Dv, nkp]); the rows of the score GEMM are (token, query head of
+// the group) pairs -- all of them meet the same keys --, S = Q . Kc^T, P = masked softmax(S) (cap, sink), O = P . V.
+static __global__ void ly_gqa_gather_kv_kernel(const uint16_t* __restrict__ pool, const int* __restrict__ page_row, int k_lo, int nk, int nkp, int E,
+                                               int koff, int D, int Dp, int voff, int Dv, uint16_t* __restrict__ kc, uint16_t* __restrict__ vt) {
+    const int r = blockIdx.x;
+    const uint16_t* src = nullptr;
+    if (r < nk) {
+        const int j = k_lo + r;
+        src = pool + ((size_t)page_row[j / kKvPage] * kKvPage + j % kKvPage) * E;
+    }
+    for (int c = threadIdx.x; c < Dp; c += blockDim.x) kc[(size_t)r * Dp + c] = (src != nullptr && c < D) ? src[koff + c] : (uint16_t)0;
+    for (int c = threadIdx.x; c < Dv; c += blockDim.x) vt[(size_t)c * nkp + r] = src != nullptr ? src[voff + c] : (uint16_t)0;
+}
+// Q operand rows (token t, head hq of group g): the prepared query times `scale`, zero padded to Dp, as hi | lo halves.  grid (nq, rep)
+static __global__ void ly_gqa_build_q_kernel(const float* __restrict__ proj, int ldp, int off_q, int row0, int rep, int g, int D, int Dp, float scale,
+                                             uint16_t* __restrict__ qhi, uint16_t* __restrict__ qlo) {
+    const int t = blockIdx.x, hq = blockIdx.y;
+    const float* qp = proj + (size_t)(row0 + t) * ldp + off_q + (size_t)(g * rep + hq) * D;
+    const size_t base = ((size_t)t * rep + hq) * Dp;
+    for (int c = threadIdx.x; c < Dp; c += blockDim.x) split_store(qhi, qlo, base + c, c < D ? qp[c] * scale : 0.f);
+}
+// o [G][nq * rep][Dv] (the value GEMMs' outputs, one slab per key/value head) -> u[row0 + t, (g rep + hq) Dv + c] and its hi | lo halves
+static __global__ void ly_gqa_scatter_kernel(const float* __restrict__ o, int nq, int G, int rep, int Dv, int row0, float* __restrict__ u,
+                                             uint16_t* __restrict__ uhi, uint16_t* __restrict__ ulo) {
+    const size_t total = (size_t)nq * G * rep * Dv;
+    const int H = G * rep;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int c = (int)(i % Dv);
+        const int hd = (int)((i / Dv) % H), t = (int)(i / ((size_t)Dv * H));
+        const int g = hd / rep, hq = hd % rep;
+        const float v = o[(((size_t)g * nq + t) * rep + hq) * Dv + c];
+        const size_t dst = ((size_t)(row0 + t) * H + hd) * Dv + c;
+        u[dst] = v;
+        split_store(uhi, ulo, dst, v);
     }
 }
 

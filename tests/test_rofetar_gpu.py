@@ -170,6 +170,27 @@ def test_tensor_core_projections(make, dtype):
     assert relerr(run_cut(model, toks, [5, 128, 129, 2, 60], cache=model.new_device_cache(4, 384)), ref) < TOL[dtype]
 
 
+def test_tensor_core_attention_long_portions():
+    """serving precision, portions of 64 tokens and more: scores and weighted sums run as tensor-core GEMMs per key/value head
+    (query heads of a group as extra rows).  Two sequences bring long portions in the same step, at positions past the start
+    and across page borders; the cap and the sink both bite (sharp scores); a short tail falls to the per-row kernel."""
+    cfg = config([att(heads=6, kv_heads=2, dim=24, vdim=40, rot_dims=8, softcap=6.0, scale=1.0, mlp=None),
+                  att(heads=4, kv_heads=2, dim=24, vdim=40, rot_dims=24, softcap=None, scale=0.3, kv_from=0, mlp=dense(ff=64))], vocab=64, width=64)
+    oracle, model = build(cfg, seed=31, dtype="bf16", tweak=_sharp)
+    a, b = tokens(cfg, 300, seed=1), tokens(cfg, 200, seed=2)
+    ra, rb = oracle.run(a), oracle.run(b)
+    cache = model.new_device_cache(max_batch=2, max_seq=320)
+    got_a, got_b = [], []
+    for (na0, na1), (nb0, nb1) in (((0, 70), (0, 3)), ((70, 199), (3, 130)), ((199, 300), (130, 200))):
+        lg = cache.forward_ragged([1, 0], [a[na0:na1], b[nb0:nb1]], [list(range(na1 - na0)), list(range(nb1 - nb0))])
+        got_a.append(lg[:na1 - na0])
+        got_b.append(lg[na1 - na0:])
+    assert relerr(np.concatenate(got_a), ra) < TOL["bf16"] and relerr(np.concatenate(got_b), rb) < TOL["bf16"]
+    # the same positions through the per-row kernel (token by token) agree with the GEMM path
+    single = run_cut(model, b, [], cache=model.new_device_cache(max_batch=1, max_seq=256))
+    assert relerr(single, rb) < TOL["bf16"]
+
+
 # ---- schedules: whole prompt, token by token, portions, batches ---------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_prefill_equals_token_by_token(dtype):
