@@ -11,6 +11,8 @@
 namespace fl {
 
 static inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
+// grouped-query attention: a launch of few (row, head) pairs splits each row's keys over up to kGqaMaxSplits blocks
+constexpr int kGqaMaxSplits = 16, kGqaSplitRows = 4 * 296;
 
 static float bits_to_f32(uint16_t b) {
     const uint32_t u = (uint32_t)b << 16;
@@ -134,6 +136,7 @@ void layered_build(LayeredModel& m, const fl_layer_desc* descs) {
             const size_t G = lw.d.kv_heads;
             lw.off_q = 0; lw.n_in = (int)(H * D); lw.off_k = lw.off_v = -1;
             reg(&lw.qnorm, D * 4);
+            m.max_av = std::max<int>(m.max_av, (int)Dv);
             if (d.kv_from < 0) {
                 lw.off_k = lw.n_in; lw.off_v = lw.off_k + (int)(G * D); lw.n_in = lw.off_v + (int)(G * Dv);
                 reg(&lw.knorm, D * 4);
@@ -481,6 +484,7 @@ void layered_cache_create(fl_cache& c, int max_slots, int max_seq, int pool_toke
         }
     }
     y.page_table.alloc((size_t)max_slots * c.pages_per_seq, true);
+    if (m.max_av > 0 && !m.f32) y.at_part.alloc((size_t)kGqaSplitRows * kGqaMaxSplits * (m.max_av + 2));
     c.slot_len.assign(max_slots, 0);
     FL_CUDA(cudaDeviceSynchronize());
 }
@@ -613,16 +617,34 @@ static void launch_gla_scan(LaunchCtx& lc, const GlaArgs& a, int n) {
     else launch(lc, "gla_scan", 0, ly_gla_scan_kernel<32>, g, b, smem, a);
 }
 
-template <typename CT>
-static void launch_gqa_attn(LaunchCtx& lc, const GqaAttnArgs& a, int T) {
-    if (T <= 0) return;
+template <typename CT, int RB>
+static void launch_gqa_attn_rb(LaunchCtx& lc, const GqaAttnArgs& a, int T, int splits) {
     const int cpl = (std::max(a.D, a.Dv) + 31) / 32;
-    const size_t smem = ((size_t)kGqaWarps * a.Dv + 2 * kGqaWarps) * 4;
-    const dim3 g(T, a.H), b(kGqaWarps * 32);
-    if (cpl <= 1) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 1>, g, b, smem, a);
-    else if (cpl <= 2) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 2>, g, b, smem, a);
-    else if (cpl <= 4) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 4>, g, b, smem, a);
-    else launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 8>, g, b, smem, a);
+    const size_t smem = ((size_t)kGqaWarps * RB * (a.Dv + 2)) * 4;
+    const dim3 g(T, a.H / RB, splits), b(kGqaWarps * 32);
+    if (cpl <= 1) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 1, RB>, g, b, smem, a);
+    else if (cpl <= 2) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 2, RB>, g, b, smem, a);
+    else if (cpl <= 4) launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 4, RB>, g, b, smem, a);
+    else launch(lc, "gqa_attn", 0, ly_gqa_attn_kernel<CT, 8, RB>, g, b, smem, a);
+}
+// max_keys: the most keys a row of the launch can see (bounds the useful number of key splits).  The exact mode never splits: there
+// a position's result is bitwise the same whatever else the launch holds.
+template <typename CT>
+static void launch_gqa_attn(LaunchCtx& lc, const GqaAttnArgs& a, int T, int max_keys, bool may_split) {
+    if (T <= 0) return;
+    const int rep = a.H / a.G, rb = rep % 4 == 0 ? 4 : (rep % 2 == 0 ? 2 : 1);
+    int splits = 1;
+    if (may_split && a.part != nullptr && (long long)T * a.H <= kGqaSplitRows) {
+        const int blocks = T * (a.H / rb);
+        splits = std::min(kGqaMaxSplits, std::max(1, 2 * kNumSMs / std::max(blocks, 1)));
+        splits = std::max(1, std::min(splits, max_keys / (kGqaWarps * 16)));        // at least 16 keys per warp
+    }
+    if (rb == 4) launch_gqa_attn_rb<CT, 4>(lc, a, T, splits);
+    else if (rb == 2) launch_gqa_attn_rb<CT, 2>(lc, a, T, splits);
+    else launch_gqa_attn_rb<CT, 1>(lc, a, T, splits);
+    if (splits > 1)
+        launch(lc, "gqa_merge", 0, ly_gqa_merge_kernel, dim3(T, a.H), dim3(std::min(256, std::max(32, (a.Dv + 31) / 32 * 32))), 0, (const float*)a.part, splits,
+               a.H, a.Dv, a.sink, a.row_base, a.out, a.ohi, a.olo);
 }
 
 template <bool DELTA>
@@ -714,7 +736,7 @@ static void gqa_attn_tc(fl_cache& c, LaunchCtx& lc, const GqaAttnArgs& a, int r0
         if (rows <= 128) {          // a short tail: the per-(row, head) kernel
             GqaAttnArgs t = a;
             t.row_base = r0 + f;
-            launch_gqa_attn<uint16_t>(lc, t, nq);
+            launch_gqa_attn<uint16_t>(lc, t, nq, p_hi, true);
             continue;
         }
         for (int g = 0; g < G; ++g) {
@@ -867,7 +889,13 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             if (m.f32) launch(lc, "attn_prep", 0, ly_attn_prep_kernel<float>, dim3(Ti), dim3(128), psm, pa);
             else launch(lc, "attn_prep", 0, ly_attn_prep_kernel<uint16_t>, dim3(Ti), dim3(128), psm, pa);
             GqaAttnArgs at{y.proj.p, lw.n_in, lw.off_q, y.kv_pool[lw.kv_index], y.page_table.p, c.pages_per_seq, st.row_seq, st.row_pos, st.seq_slot,
-                           y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0};
+                           y.u.p, lw.tc_o ? uhi : (uint16_t*)nullptr, ulo, H, G, D, Dv, d.window, d.scale, d.softcap, d.sink, 0, y.at_part.p};
+            // a step of single tokens is replayed from a captured graph whatever the contexts' lengths: its split count must not follow them
+            int max_keys = c.max_seq;
+            if (Ti != n) {
+                max_keys = 1;
+                for (int si = 0; si < n; ++si) max_keys = std::max(max_keys, h_pos0[si] + counts[si]);
+            }
             // long portions (serving precision): scores and weighted sums as tensor-core GEMMs; decoded tokens, short portions and
             // the exact mode on the per-(row, head) kernel.  Rows are taken in order.
             static const bool tc_attn_off = env_flag("FL_LAYERED_NO_TC_ATTN");
@@ -877,14 +905,14 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
                 if (m.f32 || tc_attn_off || Dv % 8 != 0 || Ts < 64 || (long long)Ts * (H / G) <= 128) continue;
                 if (r0 > done) {
                     at.row_base = done;
-                    launch_gqa_attn<uint16_t>(lc, at, r0 - done);
+                    launch_gqa_attn<uint16_t>(lc, at, r0 - done, max_keys, true);
                 }
                 gqa_attn_tc(c, lc, at, r0, Ts, h_pos0[si], slots[si]);
                 done = r0 + Ts;
             }
             if (done < Ti) {
                 at.row_base = done;
-                if (m.f32) launch_gqa_attn<float>(lc, at, Ti - done); else launch_gqa_attn<uint16_t>(lc, at, Ti - done);
+                if (m.f32) launch_gqa_attn<float>(lc, at, Ti - done, max_keys, false); else launch_gqa_attn<uint16_t>(lc, at, Ti - done, max_keys, true);
             }
         } else if (d.mixer == FL_MIXER_MAMBA2 || d.mixer == FL_MIXER_DELTA) {
             const bool delta = d.mixer == FL_MIXER_DELTA;

@@ -84,7 +84,7 @@ struct LayeredModel {
     bool finalized = false;
     uint64_t weight_bytes = 0;
     // widest sizes over the layers (workspace planning)
-    int max_in = 0, max_hv = 0, max_hd = 0, max_hc = 0, max_ff = 0, max_top = 0, max_experts = 0, max_cv = 0, max_heads = 0;
+    int max_in = 0, max_hv = 0, max_hd = 0, max_hc = 0, max_ff = 0, max_top = 0, max_experts = 0, max_cv = 0, max_heads = 0, max_av = 0;    // max_av: widest value head of a grouped-query attention layer
     std::mutex mu;
 };
 
@@ -114,6 +114,7 @@ struct LayeredCache {
     DevBuf<int> grp_cnt;
     // tensor-core latent attention of long portions: gathered keys, their transpose, Q / P operand halves, the score block
     DevBuf<uint16_t> at_kc, at_kct, at_qhi, at_qlo, at_phi, at_plo;
+    DevBuf<float> at_part;              // grouped-query attention with key splits: partial (max, sum, values) per (row, head, split)
     DevBuf<float> at_s, at_o;           // at_o: grouped-query attention, the value GEMMs' outputs per key/value head before they are interleaved
 };
 

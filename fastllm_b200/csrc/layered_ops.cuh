@@ -630,81 +630,142 @@ struct GqaAttnArgs {
     float scale, softcap;       // softcap 0 = scores are used as they are
     int sink;                   // 1: the denominator gets exp(0) more
     int row_base;
+    float* part;                // key splits (gridDim.z > 1): [T][H][splits][2 + Dv] partial (max, sum, weighted values)
 };
 constexpr int kGqaWarps = 8;
-// One block per (row, head).  score_j = cap(q . k_j * scale) over the keys j <= pos (and inside the window, if any), softmax in
-// f32 with the optional sink, out = sum_j p_j v_j.  Warp w of the eight folds keys j0 + w, j0 + w + 8, ... into an online softmax
-// (lanes own CPL consecutive channels of the key and of the value); the partial results are merged in warp order.  Which warp
-// takes which key depends on the position alone.
-template <typename CT, int CPL>
+// One block per (row, RB query heads of one key/value head, key split).  score_j = cap(q . k_j * scale) over the keys j <= pos (and
+// inside the window, if any), softmax in f32 with the optional sink, out = sum_j p_j v_j.  The 8 x splits warps of a (row, head
+// group) take the keys round-robin: warp v folds keys j0 + v, j0 + v + 8 splits, ... into an online softmax per head (lanes own
+// CPL consecutive channels of the key and of the value; a key and its value are loaded once for the RB heads).  Partial results
+// are merged in warp order; with one split the block writes the output itself (which warp takes which key then depends on the
+// position alone), otherwise ly_gqa_merge_kernel folds the splits in order.
+template <typename CT, int CPL, int RB>
 static __global__ void __launch_bounds__(kGqaWarps * 32) ly_gqa_attn_kernel(GqaAttnArgs a) {
-    extern __shared__ float sm[];               // [warps][Dv] accumulators, then [warps][2] (max, sum)
-    const int row = a.row_base + blockIdx.x, hd = blockIdx.y, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int D = a.D, Dv = a.Dv, g = hd / (a.H / a.G);
+    extern __shared__ float sm[];               // [warps][RB][Dv] accumulators, then [warps][RB][2] (max, sum)
+    const int row = a.row_base + blockIdx.x, hd0 = blockIdx.y * RB, split = blockIdx.z, S = gridDim.z;
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int D = a.D, Dv = a.Dv, g = hd0 / (a.H / a.G);
     const size_t E = (size_t)a.G * (D + Dv);
     const int pos = a.row_pos[row], slot = a.seq_slot[a.row_seq[row]];
     const int j0 = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-    float q[CPL], acc[CPL];
-    const float* qp = a.proj + (size_t)row * a.ldp + a.off_q + hd * D;
+    float q[RB][CPL], acc[RB][CPL], m[RB], l[RB];
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; q[i] = c < D ? qp[c] * a.scale : 0.f; acc[i] = 0.f; }
-    float m = -INFINITY, l = 0.f;
+    for (int r = 0; r < RB; ++r) {
+        const float* qp = a.proj + (size_t)row * a.ldp + a.off_q + (size_t)(hd0 + r) * D;
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; q[r][i] = c < D ? qp[c] * a.scale : 0.f; acc[r][i] = 0.f; }
+        m[r] = -INFINITY; l[r] = 0.f;
+    }
     const int* pt = a.page_table + (size_t)slot * a.pps;
     const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
     constexpr int KU = 2;
-    for (int j = j0 + wid; j <= pos; j += kGqaWarps * KU) {
-        float val[KU][CPL], dot[KU];
+    const int stride = kGqaWarps * S;
+    for (int j = j0 + split * kGqaWarps + wid; j <= pos; j += stride * KU) {
+        float val[KU][CPL], dot[KU][RB];
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
-            const int jj = j + u * kGqaWarps;
-            dot[u] = 0.f;
+            const int jj = j + u * stride;
+#pragma unroll
+            for (int r = 0; r < RB; ++r) dot[u][r] = 0.f;
             if (jj <= pos) {
                 const CT* kp = (const CT*)a.pool + ((size_t)pt[jj / kKvPage] * kKvPage + jj % kKvPage) * E;
                 float kk[CPL];
                 load_chunk<CPL>(kp + (size_t)g * D, lane * CPL, D, kk);
                 load_chunk<CPL>(kp + (size_t)a.G * D + (size_t)g * Dv, lane * CPL, Dv, val[u]);
 #pragma unroll
-                for (int i = 0; i < CPL; ++i) dot[u] = fmaf(q[i], kk[i], dot[u]);
+                for (int r = 0; r < RB; ++r)
+#pragma unroll
+                    for (int i = 0; i < CPL; ++i) dot[u][r] = fmaf(q[r][i], kk[i], dot[u][r]);
             } else {
 #pragma unroll
                 for (int i = 0; i < CPL; ++i) val[u][i] = 0.f;
             }
         }
 #pragma unroll
-        for (int u = 0; u < KU; ++u) dot[u] = warp_sum(dot[u]);
+        for (int u = 0; u < KU; ++u)
+#pragma unroll
+            for (int r = 0; r < RB; ++r) dot[u][r] = warp_sum(dot[u][r]);
 #pragma unroll
         for (int u = 0; u < KU; ++u) {
-            if (j + u * kGqaWarps > pos) break;
-            float sc = dot[u];
-            if (a.softcap > 0.f) sc = a.softcap * tanhf(sc * inv_cap);
-            const float mn = fmaxf(m, sc), corr = expf(m - mn), p = expf(sc - mn);
-            l = l * corr + p;
+            if (j + u * stride > pos) break;
 #pragma unroll
-            for (int i = 0; i < CPL; ++i) acc[i] = acc[i] * corr + p * val[u][i];
-            m = mn;
+            for (int r = 0; r < RB; ++r) {
+                float sc = dot[u][r];
+                if (a.softcap > 0.f) sc = a.softcap * tanhf(sc * inv_cap);
+                const float mn = fmaxf(m[r], sc), corr = expf(m[r] - mn), p = expf(sc - mn);
+                l[r] = l[r] * corr + p;
+#pragma unroll
+                for (int i = 0; i < CPL; ++i) acc[r][i] = acc[r][i] * corr + p * val[u][i];
+                m[r] = mn;
+            }
         }
     }
     float* sacc = sm;
-    float* sml = sm + kGqaWarps * Dv;
+    float* sml = sm + kGqaWarps * RB * Dv;
 #pragma unroll
-    for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; if (c < Dv) sacc[wid * Dv + c] = acc[i]; }
-    if (lane == 0) { sml[2 * wid] = m; sml[2 * wid + 1] = l; }
+    for (int r = 0; r < RB; ++r) {
+#pragma unroll
+        for (int i = 0; i < CPL; ++i) { const int c = lane * CPL + i; if (c < Dv) sacc[(wid * RB + r) * Dv + c] = acc[r][i]; }
+        if (lane == 0) { sml[(wid * RB + r) * 2] = m[r]; sml[(wid * RB + r) * 2 + 1] = l[r]; }
+    }
     __syncthreads();
-    float M = a.sink ? 0.f : -INFINITY;
+    for (int r = 0; r < RB; ++r) {
+        float M = (S == 1 && a.sink) ? 0.f : -INFINITY;
 #pragma unroll
-    for (int w = 0; w < kGqaWarps; ++w) M = fmaxf(M, sml[2 * w]);
-    float f[kGqaWarps], Lsum = a.sink ? expf(-M) : 0.f;
+        for (int w = 0; w < kGqaWarps; ++w) M = fmaxf(M, sml[(w * RB + r) * 2]);
+        float f[kGqaWarps], Lsum = (S == 1 && a.sink) ? expf(-M) : 0.f;
 #pragma unroll
-    for (int w = 0; w < kGqaWarps; ++w) { f[w] = expf(sml[2 * w] - M); Lsum += sml[2 * w + 1] * f[w]; }
-    const float inv = 1.f / Lsum;
-    const size_t ob = ((size_t)row * a.H + hd) * Dv;
+        for (int w = 0; w < kGqaWarps; ++w) {
+            const float mw = sml[(w * RB + r) * 2];
+            f[w] = mw == -INFINITY ? 0.f : expf(mw - M);       // a warp (or, with splits, a whole block) may have met no key
+            Lsum += sml[(w * RB + r) * 2 + 1] * f[w];
+        }
+        if (S == 1) {
+            const float inv = 1.f / Lsum;
+            const size_t ob = ((size_t)row * a.H + hd0 + r) * Dv;
+            for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGqaWarps; ++w) t += sacc[(w * RB + r) * Dv + c] * f[w];
+                t *= inv;
+                a.out[ob + c] = t;
+                split_store(a.ohi, a.olo, ob + c, t);
+            }
+        } else {
+            float* pp = a.part + (((size_t)blockIdx.x * a.H + hd0 + r) * S + split) * (Dv + 2);     // indexed by the row inside the launch
+            if (threadIdx.x == 0) { pp[0] = M; pp[1] = Lsum; }
+            for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < kGqaWarps; ++w) t += sacc[(w * RB + r) * Dv + c] * f[w];
+                pp[2 + c] = t;
+            }
+        }
+    }
+}
+// Folds the key splits of ly_gqa_attn_kernel in split order (and the sink): one block per (row, head).
+static __global__ void ly_gqa_merge_kernel(const float* __restrict__ part, int S, int H, int Dv, int sink, int row_base, float* __restrict__ out,
+                                           uint16_t* __restrict__ ohi, uint16_t* __restrict__ olo) {
+    const int row = row_base + blockIdx.x, hd = blockIdx.y;
+    const float* pp = part + ((size_t)blockIdx.x * H + hd) * S * (Dv + 2);
+    float M = sink ? 0.f : -INFINITY;
+    for (int s = 0; s < S; ++s) M = fmaxf(M, pp[(size_t)s * (Dv + 2)]);
+    float L = sink ? expf(-M) : 0.f;
+    for (int s = 0; s < S; ++s) {
+        const float ms = pp[(size_t)s * (Dv + 2)];
+        L += ms == -INFINITY ? 0.f : pp[(size_t)s * (Dv + 2) + 1] * expf(ms - M);
+    }
+    const float inv = 1.f / L;
+    const size_t ob = ((size_t)row * H + hd) * Dv;
     for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
         float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < kGqaWarps; ++w) t += sacc[w * Dv + c] * f[w];
+        for (int s = 0; s < S; ++s) {
+            const float ms = pp[(size_t)s * (Dv + 2)];
+            if (ms != -INFINITY) t += pp[(size_t)s * (Dv + 2) + 2 + c] * expf(ms - M);
+        }
         t *= inv;
-        a.out[ob + c] = t;
-        split_store(a.ohi, a.olo, ob + c, t);
+        out[ob + c] = t;
+        split_store(ohi, olo, ob + c, t);
     }
 }
 
