@@ -920,12 +920,14 @@ static void enqueue_step(fl_cache& c, LaunchCtx& lc, const StepTab& st, const in
             float* cstate = d.conv > 1 ? y.conv_state[lw.gla_index].p : nullptr;
             ConvArgs ca{y.proj.p, lw.n_in, lw.conv_off, lw.conv_w, lw.conv_b, cstate, st.row_seq, st.row_pos, st.seq_row0, st.seq_slot, st.seq_pos0,
                         lw.conv_ch, d.conv, y.cv.p};
+            // channel chunks per row: whole q / k heads for the delta rule (they are normalised inside one block)
+            const int chunk = delta ? D * std::max(1, 512 / D) : 512, nchunk = (lw.conv_ch + chunk - 1) / chunk;
             if (delta)
-                launch(lc, "delta_prep", 0, ly_delta_prep_kernel, dim3(Ti), dim3(256), 0, ca, lw.off_b, lw.off_a, (const float*)lw.dt_bias,
+                launch(lc, "delta_prep", 0, ly_delta_prep_kernel, dim3(Ti, nchunk), dim3(256), 0, ca, chunk, lw.off_b, lw.off_a, (const float*)lw.dt_bias,
                        (const float*)lw.a_log, H, G, D, (float)(1.0 / std::sqrt((double)D)), y.rs.p);
             else
-                launch(lc, "ssm_prep", 0, ly_mamba_prep_kernel, dim3(Ti), dim3(256), 0, ca, lw.off_dt, (const float*)lw.dt_bias, (const float*)lw.a_log, H,
-                       y.rs.p);
+                launch(lc, "ssm_prep", 0, ly_mamba_prep_kernel, dim3(Ti, nchunk), dim3(256), 0, ca, chunk, lw.off_dt, (const float*)lw.dt_bias,
+                       (const float*)lw.a_log, H, y.rs.p);
             if (d.conv > 1) launch(lc, "conv_state", 0, ly_conv_state_kernel, dim3(n, (lw.conv_ch + 127) / 128), dim3(128), 0, ca);
             // column offsets inside cv (the convolved span starts at conv_off)
             RecArgs ra{y.cv.p, lw.conv_ch, lw.off_q - lw.conv_off, lw.off_k - lw.conv_off, lw.off_v - lw.conv_off, y.rs.p,

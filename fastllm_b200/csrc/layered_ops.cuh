@@ -844,12 +844,15 @@ static __global__ void ly_conv_state_kernel(ConvArgs a) {
     for (int i = 0; i < a.taps - 1; ++i) a.state[((size_t)slot * (a.taps - 1) + i) * a.ch + c] = keep[i];
 }
 
-// Mamba-2, per row: x | B | C <- silu(conv + bias);  per head  b = softplus(dt + dt_bias),  a = exp(-exp(A_log) b)  -> ab[row, h] = (a, b)
-static __global__ void ly_mamba_prep_kernel(ConvArgs a, int off_dt, const float* __restrict__ dt_bias, const float* __restrict__ a_log, int H,
+// Mamba-2, per row: x | B | C <- silu(conv + bias);  per head  b = softplus(dt + dt_bias),  a = exp(-exp(A_log) b)  -> ab[row, h] = (a, b).
+// grid (rows, channel chunks of `chunk`): the first chunk's block also computes the per-head scalars.
+static __global__ void ly_mamba_prep_kernel(ConvArgs a, int chunk, int off_dt, const float* __restrict__ dt_bias, const float* __restrict__ a_log, int H,
                                             float* __restrict__ ab) {
     const int row = blockIdx.x, seq = a.row_seq[row], pos = a.row_pos[row];
     const int row0 = a.seq_row0[seq], pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
-    for (int c = threadIdx.x; c < a.ch; c += blockDim.x) a.cv[(size_t)row * a.ch + c] = conv_silu(a, row, row0, pos, pos0, slot, c);
+    const int c0 = blockIdx.y * chunk, c1 = min(a.ch, c0 + chunk);
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) a.cv[(size_t)row * a.ch + c] = conv_silu(a, row, row0, pos, pos0, slot, c);
+    if (blockIdx.y != 0) return;
     for (int h = threadIdx.x; h < H; h += blockDim.x) {
         const float dt = softplusf_(a.proj[(size_t)row * a.ldp + off_dt + h] + dt_bias[h]);
         ab[((size_t)row * H + h) * 2] = expf(-expf(a_log[h]) * dt);
@@ -858,21 +861,26 @@ static __global__ void ly_mamba_prep_kernel(ConvArgs a, int off_dt, const float*
 }
 
 // Gated delta rule, per row: q | k | v <- silu(conv);  q, k heads -> unit vectors (x / sqrt(sum x^2 + 1e-6)), q also times qscale;
-// per head  b = sigmoid(proj[off_b + h]),  a = exp(-exp(A_log) softplus(proj[off_a + h] + dt_bias))  -> ab[row, h] = (a, b)
-static __global__ void ly_delta_prep_kernel(ConvArgs a, int off_b, int off_a, const float* __restrict__ dt_bias, const float* __restrict__ a_log, int H,
-                                            int G, int D, float qscale, float* __restrict__ ab) {
+// per head  b = sigmoid(proj[off_b + h]),  a = exp(-exp(A_log) softplus(proj[off_a + h] + dt_bias))  -> ab[row, h] = (a, b).
+// grid (rows, channel chunks of `chunk`, a multiple of D: a q or k head never straddles two blocks).
+static __global__ void ly_delta_prep_kernel(ConvArgs a, int chunk, int off_b, int off_a, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
+                                            int H, int G, int D, float qscale, float* __restrict__ ab) {
     const int row = blockIdx.x, seq = a.row_seq[row], pos = a.row_pos[row];
     const int row0 = a.seq_row0[seq], pos0 = a.seq_pos0[seq], slot = a.seq_slot[seq];
+    const int c0 = blockIdx.y * chunk, c1 = min(a.ch, c0 + chunk);
     float* cvr = a.cv + (size_t)row * a.ch;
-    for (int c = threadIdx.x; c < a.ch; c += blockDim.x) cvr[c] = conv_silu(a, row, row0, pos, pos0, slot, c);
-    for (int h = threadIdx.x; h < H; h += blockDim.x) {
-        const float* pr = a.proj + (size_t)row * a.ldp;
-        ab[((size_t)row * H + h) * 2] = expf(-expf(a_log[h]) * softplusf_(pr[off_a + h] + dt_bias[h]));
-        ab[((size_t)row * H + h) * 2 + 1] = sigmoidf_(pr[off_b + h]);
+    for (int c = c0 + threadIdx.x; c < c1; c += blockDim.x) cvr[c] = conv_silu(a, row, row0, pos, pos0, slot, c);
+    if (blockIdx.y == 0) {
+        for (int h = threadIdx.x; h < H; h += blockDim.x) {
+            const float* pr = a.proj + (size_t)row * a.ldp;
+            ab[((size_t)row * H + h) * 2] = expf(-expf(a_log[h]) * softplusf_(pr[off_a + h] + dt_bias[h]));
+            ab[((size_t)row * H + h) * 2 + 1] = sigmoidf_(pr[off_b + h]);
+        }
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int it = wid; it < 2 * G; it += nw) {          // q heads, then k heads
+    const int h0 = c0 / D, h1 = min(2 * G, c1 / D);         // q heads, then k heads, of this chunk
+    for (int it = h0 + wid; it < h1; it += nw) {
         float* v = cvr + (size_t)it * D;
         float ss = 0.f;
         for (int c = lane; c < D; c += 32) ss += v[c] * v[c];
