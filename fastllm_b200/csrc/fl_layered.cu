@@ -649,16 +649,17 @@ static void launch_gqa_attn(LaunchCtx& lc, const GqaAttnArgs& a, int T, int max_
 
 template <bool DELTA>
 static void launch_rec_scan(LaunchCtx& lc, const RecArgs& a, int n) {
-    const int rpt = (a.D + kGlaDG - 1) / kGlaDG;
-    const size_t smem = ((size_t)4 * a.D + 2 * kGlaVS + 4 + 3 * kGlaDG * kGlaVS) * 4;
-    const dim3 g(n, a.H, (a.Dv + kGlaVS - 1) / kGlaVS), b(kGlaVS * kGlaDG);
-    const char* tag = DELTA ? "delta_scan" : "ssm_scan";
-    if (rpt <= 1) launch(lc, tag, 0, ly_rec_scan_kernel<1, DELTA>, g, b, smem, a);
-    else if (rpt <= 2) launch(lc, tag, 0, ly_rec_scan_kernel<2, DELTA>, g, b, smem, a);
-    else if (rpt <= 4) launch(lc, tag, 0, ly_rec_scan_kernel<4, DELTA>, g, b, smem, a);
-    else if (rpt <= 8) launch(lc, tag, 0, ly_rec_scan_kernel<8, DELTA>, g, b, smem, a);
-    else if (rpt <= 16) launch(lc, tag, 0, ly_rec_scan_kernel<16, DELTA>, g, b, smem, a);
-    else launch(lc, tag, 0, ly_rec_scan_kernel<32, DELTA>, g, b, smem, a);
+    const int rpt = (a.D + kRecParts - 1) / kRecParts;
+    auto go = [&](auto kern, int RPT) {
+        const size_t smem = (size_t)4 * (RPT >= 64 ? 4 : 8) * (2 * kRecParts * (RPT + 4) + 12) * 4;       // [4 warps][ring][slot] floats
+        launch(lc, DELTA ? "delta_scan" : "ssm_scan", 0, kern, dim3(n, a.H, (a.Dv + kRecCols - 1) / kRecCols), dim3(128), smem, a);
+    };
+    if (rpt <= 2) go(ly_rec_scan_kernel<2, DELTA>, 2);
+    else if (rpt <= 4) go(ly_rec_scan_kernel<4, DELTA>, 4);
+    else if (rpt <= 8) go(ly_rec_scan_kernel<8, DELTA>, 8);
+    else if (rpt <= 16) go(ly_rec_scan_kernel<16, DELTA>, 16);
+    else if (rpt <= 32) go(ly_rec_scan_kernel<32, DELTA>, 32);
+    else go(ly_rec_scan_kernel<64, DELTA>, 64);
 }
 
 // Latent attention of rows [r0, r0 + Ts) -- one sequence's portion, positions pos0.. -- on the tensor-core GEMM, in blocks of query

@@ -9,6 +9,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace fl {
 
@@ -898,76 +899,89 @@ struct RecArgs {
     const int *seq_row0, *seq_slot, *seq_pos0;
     int H, G, D, Dv;
 };
+constexpr int kRecCols = 32, kRecParts = 4;       // value columns per block; threads that share a column's rows
 // Token by token, per head:  S <- a S;  u = b v   (DELTA: u = b (v - S^T k));  S <- S + k u^T;  o = S^T q (+ dskip v).
-// One block per (sequence, head, 32 value columns) -- columns of S never interact; thread (vcol, dg) keeps rows dg, dg + 8, ... of its
-// column in registers.  The next token's operands travel into registers while the current one is folded.  The order of operations per
-// token does not depend on how a prompt was cut.
+// One block of four warps per (sequence, head, 32 value columns) -- columns of S never interact.  A column's rows are split over
+// four neighbouring lanes (lane part p keeps rows p RPT .. p RPT + RPT - 1 in registers), so the two reductions over rows are a
+// serial sum per lane and two shuffles: the warps of a block never wait for one another.  Each warp keeps a ring of the next
+// tokens' operands (k, q, its eight values, a, b) in its own shared memory, filled by asynchronous copies several tokens ahead,
+// so a token's step waits for no global load.  The order of operations per token does not depend on how a prompt was cut.
 template <int RPT, bool DELTA>
-static __global__ void __launch_bounds__(kGlaVS * kGlaDG) ly_rec_scan_kernel(RecArgs a) {
-    extern __shared__ float sm[];
+static __global__ void __launch_bounds__(128) ly_rec_scan_kernel(RecArgs a) {
+    extern __shared__ __align__(16) float sm[]; // [4 warps][NST tokens][k | q: 4 parts x (RPT + 4) each (the pad keeps the parts on different banks) | v x 8 | a | b | pad]
+    constexpr int DP = RPT * kRecParts;         // rows, padded (rows >= D hold zeros and never change)
+    constexpr int PS = RPT + 4, DPS = kRecParts * PS;      // floats per part / per vector in shared memory
+    constexpr int NST = RPT >= 64 ? 4 : 8;      // tokens in the ring
+    constexpr int SLOT = 2 * DPS + 12;
+    constexpr int NL = (2 * DP + 31) / 32;      // k | q values a lane copies per token
     const int D = a.D, Dv = a.Dv;
-    float* sq = sm;                     // [2][D]
-    float* sk = sq + 2 * D;             // [2][D]
-    float* sv = sk + 2 * D;             // [2][32]
-    float* sab = sv + 2 * kGlaVS;       // [2][2]
-    float* red = sab + 4;               // [2][8][32] read-out partials
-    float* red1 = red + 2 * kGlaDG * kGlaVS;    // [8][32] S^T k partials (DELTA)
-    const int seq = blockIdx.x, hd = blockIdx.y, v0 = blockIdx.z * kGlaVS, g = hd / (a.H / a.G);
-    const int tid = threadIdx.x, vc = tid & 31, dg = tid >> 5;
+    const int seq = blockIdx.x, hd = blockIdx.y, g = hd / (a.H / a.G);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, p = lane & 3, cl = lane >> 2;
+    const int col0 = blockIdx.z * kRecCols + wid * 8, col = col0 + cl;
+    const bool vok = col < Dv;
+    float* wsm = sm + wid * (NST * SLOT);
     const int r0 = a.seq_row0[seq], r1 = a.seq_row0[seq + 1];
-    const bool vok = v0 + vc < Dv;
-    float* st = a.state + (((size_t)a.seq_slot[seq] * a.H + hd) * D) * Dv + v0 + vc;
+    float* st = a.state + (((size_t)a.seq_slot[seq] * a.H + hd) * D) * Dv + col;
     float s[RPT];
     const bool fresh = a.seq_pos0[seq] == 0;
 #pragma unroll
     for (int i = 0; i < RPT; ++i) {
-        const int d = dg + kGlaDG * i;
+        const int d = p * RPT + i;
         s[i] = (!fresh && vok && d < D) ? st[(size_t)d * Dv] : 0.f;
     }
-    const bool ld_d = tid < D, ld_v = tid < kGlaVS, ld_s = tid >= 32 && tid < 34;
     const float dsk = a.dskip ? a.dskip[hd] : 0.f;
-    float rq = 0.f, rk = 0.f, rv = 0.f, rs = 0.f;
-    auto fetch = [&](int row) {
+    for (int i = lane; i < NST * SLOT; i += 32) wsm[i] = 0.f;       // what no copy ever writes (rows >= D, columns >= Dv) reads as zero
+    __syncwarp();
+    auto issue = [&](int row, int slot) {
         const float* pr = a.cv + (size_t)row * a.ldc;
-        if (ld_d) { rq = pr[a.off_q + g * D + tid]; rk = pr[a.off_k + g * D + tid]; }
-        if (ld_v) rv = (v0 + tid < Dv) ? pr[a.off_v + hd * Dv + v0 + tid] : 0.f;
-        if (ld_s) rs = a.ab[((size_t)row * a.H + hd) * 2 + (tid - 32)];
-    };
-    auto stage = [&](int b) {
-        if (ld_d) { sq[b * D + tid] = rq; sk[b * D + tid] = rk; }
-        if (ld_v) sv[b * kGlaVS + tid] = rv;
-        if (ld_s) sab[b * 2 + (tid - 32)] = rs;
-    };
-    auto finish = [&](int row, int b) {
-        if (dg == 0 && vok) {
-            const float* rp = red + b * kGlaDG * kGlaVS;
-            float t = 0.f;
+        float* dst = wsm + slot * SLOT;
 #pragma unroll
-            for (int k = 0; k < kGlaDG; ++k) t += rp[k * kGlaVS + vc];
-            a.o[(size_t)row * a.H * Dv + hd * Dv + v0 + vc] = t + dsk * sv[b * kGlaVS + vc];
+        for (int t = 0; t < NL; ++t) {
+            const int idx = lane + 32 * t, isq = idx >= DP, d = idx - isq * DP;
+            if (idx < 2 * DP && d < D) cp_async_f32(dst + isq * DPS + (d / RPT) * PS + d % RPT, pr + (isq ? a.off_q : a.off_k) + g * D + d);
+        }
+        if (lane < 8) {
+            if (col0 + lane < Dv) cp_async_f32(dst + 2 * DPS + lane, pr + a.off_v + hd * Dv + col0 + lane);
+        } else if (lane < 10) {
+            cp_async_f32(dst + 2 * DPS + lane, a.ab + ((size_t)row * a.H + hd) * 2 + (lane - 8));
         }
     };
-    if (r0 < r1) { fetch(r0); stage(0); }
-    int b = 0;
-    for (int row = r0; row < r1; ++row, b ^= 1) {
-        if (row + 1 < r1) fetch(row + 1);
-        __syncthreads();
-        if (row > r0) finish(row - 1, b ^ 1);
-        const float v = sv[b * kGlaVS + vc], da = sab[b * 2], db = sab[b * 2 + 1];
+#pragma unroll
+    for (int t = 0; t < NST - 1; ++t) {
+        if (r0 + t < r1) issue(r0 + t, t);
+        cp_async_commit();
+    }
+    int it = 0;
+    for (int row = r0; row < r1; ++row, ++it) {
+        if (row + NST - 1 < r1) issue(row + NST - 1, (it + NST - 1) % NST);
+        cp_async_commit();
+        cp_async_wait<NST - 1>();               // this token's copies have landed (one group per token, empty ones included)
+        __syncwarp();
+        const float* cur = wsm + (it % NST) * SLOT;
+        const float v = cur[2 * DPS + cl], da = cur[2 * DPS + 8], db = cur[2 * DPS + 9];
+        float kb[RPT], qb[RPT];                 // this lane's rows of k and q
+        {
+            const float* ks = cur + p * PS;
+            if (RPT % 4 == 0) {
+#pragma unroll
+                for (int i = 0; i < RPT / 4; ++i) {
+                    const float4 k4 = reinterpret_cast<const float4*>(ks)[i], q4 = reinterpret_cast<const float4*>(ks + DPS)[i];
+                    kb[4 * i] = k4.x; kb[4 * i + 1] = k4.y; kb[4 * i + 2] = k4.z; kb[4 * i + 3] = k4.w;
+                    qb[4 * i] = q4.x; qb[4 * i + 1] = q4.y; qb[4 * i + 2] = q4.z; qb[4 * i + 3] = q4.w;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < RPT; ++i) { kb[i] = ks[i]; qb[i] = ks[DPS + i]; }
+            }
+        }
         float u;
         if (DELTA) {
             float part = 0.f;
 #pragma unroll
-            for (int i = 0; i < RPT; ++i) {
-                const int d = dg + kGlaDG * i;
-                if (d < D) { s[i] *= da; part = fmaf(s[i], sk[b * D + d], part); }
-            }
-            red1[dg * kGlaVS + vc] = part;
-            __syncthreads();
-            float r = 0.f;
-#pragma unroll
-            for (int k = 0; k < kGlaDG; ++k) r += red1[k * kGlaVS + vc];
-            u = db * (v - r);
+            for (int i = 0; i < RPT; ++i) { s[i] *= da; part = fmaf(s[i], kb[i], part); }
+            part += __shfl_xor_sync(0xFFFFFFFFu, part, 1);
+            part += __shfl_xor_sync(0xFFFFFFFFu, part, 2);
+            u = db * (v - part);
         } else {
 #pragma unroll
             for (int i = 0; i < RPT; ++i) s[i] *= da;
@@ -976,21 +990,19 @@ static __global__ void __launch_bounds__(kGlaVS * kGlaDG) ly_rec_scan_kernel(Rec
         float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
-            const int d = dg + kGlaDG * i;
-            if (d < D) {
-                s[i] = fmaf(sk[b * D + d], u, s[i]);
-                acc = fmaf(s[i], sq[b * D + d], acc);
-            }
+            s[i] = fmaf(kb[i], u, s[i]);
+            acc = fmaf(s[i], qb[i], acc);
         }
-        red[(b * kGlaDG + dg) * kGlaVS + vc] = acc;
-        if (row + 1 < r1) stage(b ^ 1);
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
+        if (p == 0 && vok) a.o[(size_t)row * a.H * Dv + hd * Dv + col] = acc + dsk * v;
+        __syncwarp();                           // the slot may be refilled in the next iteration
     }
-    __syncthreads();
-    if (r0 < r1) finish(r1 - 1, b ^ 1);
+    cp_async_wait<0>();
     if (vok) {
 #pragma unroll
         for (int i = 0; i < RPT; ++i) {
-            const int d = dg + kGlaDG * i;
+            const int d = p * RPT + i;
             if (d < D) st[(size_t)d * Dv] = s[i];
         }
     }
