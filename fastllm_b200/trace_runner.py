@@ -58,6 +58,8 @@ def main(argv=None) -> int:
                 if not free:
                     raise RuntimeError("more live requests than sequence slots")
                 slot_of[e["id"]] = free.pop()
+            if not e.get("tokens"):
+                continue                # admitted, nothing to feed in this step
             slots.append(slot_of[e["id"]])
             toks.append(e["tokens"])
             want.append(e.get("want", []))
