@@ -415,6 +415,24 @@ def test_checkpoint_folder_through_the_registry(tmp_path):
     assert relerr(run_whole(model, toks), O.Rofetar(cfg, w).run(toks)) < TOL["f32"]
 
 
+def test_command_line_generate(tmp_path):
+    """python -m fastllm_b200 generate: registry, loader, continuous batcher with prompt portions, greedy sampling -- ids in, ids out"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = hybrid_cfg()
+    w = O.random_weights(cfg, 29)
+    _write_checkpoint(tmp_path / "m", cfg, w)
+    prompts = [tokens(cfg, n, seed=60 + n) for n in (3, 40, 17)]
+    cmd = ["python3", "-m", "fastllm_b200", "generate", "--model", str(tmp_path / "m"), "--dtype", "f32", "--max-tokens", "6", "--max-batch", "2",
+           "--prefill-chunk", "16"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(str(t) for t in p)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, cwd=root, env=dict(os.environ, PYTHONPATH=root))
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [json.loads(l)["generated"] for l in r.stdout.splitlines() if l.startswith("{")]
+    oracle = O.Rofetar(cfg, w)
+    assert got == [oracle_greedy(oracle, p, 6) for p in prompts]
+
+
 def test_trace_runner_end_to_end(tmp_path):
     """bin/trace_run as a process: steps on standard input (portions beside single tokens, a request that sits out a step, one that
     wants nothing, a fifth request that takes over a finished one's slot and pages), logits files out"""
