@@ -13,6 +13,8 @@ namespace fl {
 static inline size_t up256(size_t x) { return (x + 255) / 256 * 256; }
 // grouped-query attention: a launch of few (row, head) pairs splits each row's keys over up to kGqaMaxSplits blocks
 constexpr int kGqaMaxSplits = 16, kGqaSplitRows = 4 * 296;
+// the softmax between the two attention GEMMs keeps a row's scores in shared memory when the row has at most this many visible keys
+constexpr int kSoftmaxKeep = 10240;
 
 static float bits_to_f32(uint16_t b) {
     const uint32_t u = (uint32_t)b << 16;
@@ -700,8 +702,9 @@ static void latent_attn_tc(fl_cache& c, LaunchCtx& lc, const LayeredLayerW& lw, 
                y.at_qhi.p, y.at_qlo.p);
         const CUtensorMap tk = make_tmap_bf16(y.at_kc.p, (uint64_t)nkp, (uint64_t)Ep, (uint64_t)Ep, 128);
         dense_gemm(c, lc, "gemm_tc_attn_scores", rows, nkp, Ep, tk, y.at_s.p, y.at_qhi.p, y.at_qlo.p);
-        launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), 0, (const float*)y.at_s.p, a.row_pos, r0 + f, H, k_lo, nk, nkp, a.window,
-               0.f, 0, y.at_phi.p, y.at_plo.p);
+        const int keep = std::min(nkp, kSoftmaxKeep);
+        launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), (size_t)keep * 4, (const float*)y.at_s.p, a.row_pos, r0 + f, H, k_lo, nk, nkp,
+               a.window, 0.f, 0, keep, y.at_phi.p, y.at_plo.p);
         const CUtensorMap tv = make_tmap_bf16(y.at_kct.p, (uint64_t)C, (uint64_t)nkp, (uint64_t)nkp, 128);
         dense_gemm(c, lc, "gemm_tc_attn_values", rows, C, nkp, tv, a.ol + (size_t)(r0 + f) * H * C, y.at_phi.p, y.at_plo.p);
     }
@@ -747,8 +750,9 @@ static void gqa_attn_tc(fl_cache& c, LaunchCtx& lc, const GqaAttnArgs& a, int r0
                    y.at_qlo.p);
             const CUtensorMap tk = make_tmap_bf16(y.at_kc.p, (uint64_t)nkp, (uint64_t)Dp, (uint64_t)Dp, 128);
             dense_gemm(c, lc, "gemm_tc_attn_scores", rows, nkp, Dp, tk, y.at_s.p, y.at_qhi.p, y.at_qlo.p);
-            launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), 0, (const float*)y.at_s.p, a.row_pos, r0 + f, rep, k_lo, nk, nkp, a.window,
-                   a.softcap, a.sink, y.at_phi.p, y.at_plo.p);
+            const int keep = std::min(nkp, kSoftmaxKeep);
+            launch(lc, "attn_softmax", 0, ly_attn_softmax_kernel, dim3(rows), dim3(256), (size_t)keep * 4, (const float*)y.at_s.p, a.row_pos, r0 + f, rep, k_lo, nk, nkp,
+                   a.window, a.softcap, a.sink, keep, y.at_phi.p, y.at_plo.p);
             const CUtensorMap tv = make_tmap_bf16(y.at_kct.p, (uint64_t)Dv, (uint64_t)nkp, (uint64_t)nkp, 128);
             dense_gemm(c, lc, "gemm_tc_attn_values", rows, Dv, nkp, tv, y.at_o.p + (size_t)g * rows * Dv, y.at_phi.p, y.at_plo.p);
         }

@@ -531,8 +531,11 @@ static __global__ void ly_attn_build_q_kernel(const float* __restrict__ qa, cons
 }
 // P[r, col] = softmax over the keys the row's position admits (0 <= pos - j < window, j = k_lo + col), zero elsewhere; row r belongs
 // to token r / H of the block.  softcap > 0: scores pass softcap * tanh(s / softcap) first; sink: the denominator gets exp(0) more.
+// The (capped) scores of the row are kept in shared memory after the first pass when `keep` floats of it were given to the launch
+// and the row fits (a thread meets the same columns in every pass, so it reads back what it wrote itself).
 static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const int* __restrict__ row_pos, int row0, int H, int k_lo, int nk, int nkp,
-                                              int window, float softcap, int sink, uint16_t* __restrict__ phi, uint16_t* __restrict__ plo) {
+                                              int window, float softcap, int sink, int keep, uint16_t* __restrict__ phi, uint16_t* __restrict__ plo) {
+    extern __shared__ float srow[];
     __shared__ float red[33];
     const size_t r = blockIdx.x;
     const int pos = row_pos[row0 + (int)(r / H)];
@@ -540,9 +543,14 @@ static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const
     const int c_lo = j_first > k_lo ? j_first - k_lo : 0, c_hi = min(nk, pos - k_lo + 1);      // visible columns [c_lo, c_hi)
     const float* sr = S + r * nkp;
     const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    const bool kept = c_hi - c_lo <= keep;
     auto score = [&](int c) { const float v = sr[c]; return softcap > 0.f ? softcap * tanhf(v * inv_cap) : v; };
     float m = sink ? 0.f : -INFINITY;
-    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) m = fmaxf(m, score(c));
+    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
+        const float v = score(c);
+        if (kept) srow[c - c_lo] = v;
+        m = fmaxf(m, v);
+    }
     m = warp_max(m);
     {
         const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
@@ -553,10 +561,15 @@ static __global__ void ly_attn_softmax_kernel(const float* __restrict__ S, const
         m = warp_max(t);
     }
     float sum = 0.f;
-    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) sum += expf(score(c) - m);
+    for (int c = c_lo + threadIdx.x; c < c_hi; c += blockDim.x) {
+        const float e = expf((kept ? srow[c - c_lo] : score(c)) - m);
+        if (kept) srow[c - c_lo] = e;
+        sum += e;
+    }
     const float inv = 1.f / (block_sum(sum, red) + (sink ? expf(-m) : 0.f));
     for (int c = threadIdx.x; c < nkp; c += blockDim.x) {
-        const float p = (c >= c_lo && c < c_hi) ? expf(score(c) - m) * inv : 0.f;
+        float p = 0.f;
+        if (c >= c_lo && c < c_hi) p = (kept ? srow[c - c_lo] : expf(score(c) - m)) * inv;
         split_store(phi, plo, r * nkp + c, p);
     }
 }
